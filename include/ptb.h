@@ -1,0 +1,192 @@
+/*
+ * ptb.h -- C ABI of the B200 (sm_100a) FP8 quantize / GEMM / grouped-GEMM library.
+ *
+ * Every entry point takes raw device pointers, explicit sizes/strides and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t).  The library owns no memory: the caller allocates
+ * every output and workspace.  All work is enqueued on the given stream; no call synchronises
+ * the host with the device.  Calls are re-entrant and keep no state between calls.
+ *
+ * Return value: 0 on success; a negative value for an argument error (PTB_ERR_*); a positive
+ * value is a cudaError_t reported by the CUDA runtime or driver.  ptb_last_error() returns a
+ * description of the last failure on the calling thread.
+ *
+ * Each declaration names the interface of the reference project (Primus-Turbo) it replaces,
+ * as file:line inside that project.
+ */
+#ifndef PTB_H_
+#define PTB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PTB_VERSION 100
+
+typedef void *ptb_stream_t; /* cudaStream_t */
+
+/* element types */
+#define PTB_F32 0
+#define PTB_F16 1
+#define PTB_BF16 2
+#define PTB_E4M3 3 /* float8_e4m3fn (OCP), max 448   */
+#define PTB_E5M2 4 /* float8_e5m2   (OCP), max 57344 */
+
+/* scaling granularity; values match ScalingGranularity in
+ * primus_turbo/pytorch/core/low_precision.py:125-133 */
+#define PTB_TENSORWISE 1
+#define PTB_ROWWISE 2
+#define PTB_BLOCKWISE 3
+
+/* argument errors */
+#define PTB_ERR_ARG (-1)         /* null pointer, negative size, unknown enum         */
+#define PTB_ERR_UNSUPPORTED (-2) /* valid request outside what the kernels implement  */
+#define PTB_ERR_ALIGN (-3)       /* pointer / leading dimension not 16-byte aligned   */
+#define PTB_ERR_DRIVER (-4)      /* CUDA driver entry point unavailable               */
+#define PTB_ERR_TOO_LARGE (-5)   /* size beyond a stated static limit                 */
+
+int ptb_version(void);
+const char *ptb_last_error(void);
+
+/* ------------------------------------------------------------------ quantize ----------------- */
+
+/* Bytes of workspace ptb_quant_fp8_tensorwise needs (one amax word, padded). */
+#define PTB_TENSORWISE_WS_BYTES 256
+
+/* Tensorwise: amax over all n elements, scale = fmax/max(amax,1e-12), scale_inv = 1/scale,
+ * q = cast(clamp(x*scale)).  Writes q[n] and scale_inv[1].  workspace: PTB_TENSORWISE_WS_BYTES,
+ * cleared by the call itself.
+ * Replaces torch op quantize_fp8_tensorwise (csrc/pytorch/bindings_pytorch.cpp:31,
+ * csrc/pytorch/quantization/quantization.cpp:42-88). */
+int ptb_quant_fp8_tensorwise(const void *x, int x_dtype, int64_t n, void *q, int q_dtype,
+                             float *scale_inv, void *workspace, ptb_stream_t stream);
+
+/* Tensorwise with a caller-given scale (device scalar): scale_inv = 1/scale.
+ * Replaces the scale_opt branch of quantize_fp8_tensorwise (quantization.cpp:53-56). */
+int ptb_quant_fp8_tensorwise_with_scale(const void *x, int x_dtype, int64_t n, const float *scale,
+                                        void *q, int q_dtype, float *scale_inv,
+                                        ptb_stream_t stream);
+
+/* Rowwise: x viewed as [B, M, N], one scale per (b, n) over the M axis; scale_inv is [B,1,N].
+ * N == 1 is the "axis is the last dimension" case.  workspace: B*N floats (only read when
+ * N > 1; cleared by the call).
+ * Replaces torch op quantize_fp8_rowwise (bindings_pytorch.cpp:33, quantization.cpp:108-206). */
+int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, void *q,
+                          int q_dtype, float *scale_inv, void *workspace, ptb_stream_t stream);
+
+/* 1-D blockwise (block = 128): axis 1 -> scale_inv [M, ceil(N/128)]; axis 0 -> [ceil(M/128), N].
+ * Replaces primus_turbo::quant_fp8_blockwise_impl
+ * (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:74-118). */
+int ptb_quant_fp8_block1d(const void *x, int x_dtype, int64_t M, int64_t N, int axis, void *q,
+                          int q_dtype, float *scale_inv, ptb_stream_t stream);
+
+/* Both 1-D blockwise copies from one read of x; both copies are [M,N] (not transposed).
+ * Replaces primus_turbo::quant_fp8_blockwise_dual_impl (quantization_impl.py:229-274). */
+int ptb_quant_fp8_block1d_dual(const void *x, int x_dtype, int64_t M, int64_t N, void *q_row,
+                               float *s_row, void *q_col, float *s_col, int q_dtype,
+                               ptb_stream_t stream);
+
+/* 2-D blockwise (one scale per 128x128 tile) of w [B, M, N]; scale_inv [B, ceil(M/128),
+ * ceil(N/128)].  Replaces torch op quantize_fp8_blockwise_for_weight
+ * (bindings_pytorch.cpp:37, quantization.cpp:1442-1476). */
+int ptb_quant_fp8_block2d(const void *w, int w_dtype, int64_t B, int64_t M, int64_t N, void *q,
+                          int q_dtype, float *scale_inv, ptb_stream_t stream);
+
+/* Grouped activation quantize, one read of x [M, N]:
+ *   q_row [M, N], s_row [ceil(N/128), M] (row scales stored transposed);
+ *   q_col_padded [M + 128*G, N]: group g occupies rows [var_k_offs[g], +len_g) followed by zero
+ *   rows up to a multiple of 128; s_col_padded [ceil((M+128*G)/128), N] on group-relative
+ *   128-row blocks; var_k_lens[G] = ceil(len/128)*128 and its exclusive prefix var_k_offs[G+1].
+ * Rows at or beyond group_offs[G] (row outputs) / var_k_offs[G] (padded outputs) are not written.
+ * Replaces torch op quantize_fp8_blockwise_segment_m_row_col (bindings_pytorch.cpp:35,
+ * quantization.cpp:1382-1439). */
+int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t N, int64_t G,
+                                  const int64_t *group_lens, const int64_t *group_offs,
+                                  void *q_row, void *q_col_padded, float *s_row,
+                                  float *s_col_padded, int64_t *var_k_lens, int64_t *var_k_offs,
+                                  int q_dtype, ptb_stream_t stream);
+
+/* ------------------------------------------------------------------ dequantize --------------- */
+/* out = cast(float(q) * scale_inv).  Replace dequantize_fp8_tensorwise / dequantize_fp8_rowwise
+ * (bindings_pytorch.cpp:43-46) and primus_turbo::dequant_fp8_blockwise_impl /
+ * dequant_fp8_blockwise_for_weight_impl (quantization_impl.py:139-227). */
+int ptb_dequant_fp8_tensorwise(const void *q, int q_dtype, int64_t n, const float *scale_inv,
+                               void *out, int out_dtype, ptb_stream_t stream);
+int ptb_dequant_fp8_rowwise(const void *q, int q_dtype, int64_t B, int64_t M, int64_t N,
+                            const float *scale_inv, void *out, int out_dtype, ptb_stream_t stream);
+int ptb_dequant_fp8_block1d(const void *q, int q_dtype, int64_t M, int64_t N, int axis,
+                            const float *scale_inv, void *out, int out_dtype, ptb_stream_t stream);
+int ptb_dequant_fp8_block2d(const void *q, int q_dtype, int64_t B, int64_t M, int64_t N,
+                            const float *scale_inv, void *out, int out_dtype, ptb_stream_t stream);
+
+/* ------------------------------------------------------------------ helpers ------------------ */
+/* Exclusive prefix sum of int64 group lengths: offs[G+1].
+ * Replaces torch op grouped_gemm_compute_offs (bindings_pytorch.cpp:129,
+ * csrc/pytorch/grouped_gemm/ck_grouped_gemm.cpp:63-80). */
+int ptb_group_offs(const int64_t *group_lens, int64_t G, int64_t *group_offs, ptb_stream_t stream);
+
+/* Byte transpose [B, M, N] -> [B, N, M] of 1-byte elements.
+ * Replaces torch op transpose_2d (bindings_pytorch.cpp:41) for FP8 payloads. */
+int ptb_transpose_2d_u8(const void *in, int64_t B, int64_t M, int64_t N, void *out,
+                        ptb_stream_t stream);
+
+/* ------------------------------------------------------------------ GEMM --------------------- */
+/* C[M,N] = op(A)[M,K] . op(B)[K,N], FP8 operands, fp32 accumulation, c_dtype output.
+ *   a: [M,K] (trans_a = 0, lda = row pitch in elements) or [K,M] (trans_a = 1)
+ *   b: [K,N] (trans_b = 0) or [N,K] (trans_b = 1)
+ * granularity:
+ *   PTB_TENSORWISE  C = acc * (a_scale[0]*b_scale[0])
+ *   PTB_ROWWISE     C = acc * (a_scale[m*a_scale_stride_m] * b_scale[n*b_scale_stride_n])
+ *   PTB_BLOCKWISE   per 128-wide contraction block kb:
+ *        acc += partial_kb * a_scale[m*a_scale_stride_m + kb*a_scale_stride_k]
+ *                          * b_scale[(b_block_2d ? n/128 : n)*b_scale_stride_n + kb*b_scale_stride_k]
+ * Pointers and leading dimensions must be 16-byte aligned.  num_sms <= 0 uses every SM.
+ * Replaces primus_turbo::gemm_fp8_impl
+ * (primus_turbo/pytorch/kernels/gemm/gemm_fp8_impl.py:438-467), i.e. the torch ops
+ * hipblaslt_gemm_fp8 and ck_gemm_fp8 (csrc/pytorch/gemm/ck_gemm.cpp:32-98) and the Triton
+ * kernels in primus_turbo/triton/gemm/gemm_fp8_kernel.py. */
+int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const void *b, int b_dtype,
+                 int trans_b, int64_t ldb, void *c, int c_dtype, int64_t ldc, int64_t M, int64_t N,
+                 int64_t K, int granularity, const float *a_scale, int64_t a_scale_stride_m,
+                 int64_t a_scale_stride_k, const float *b_scale, int64_t b_scale_stride_n,
+                 int64_t b_scale_stride_k, int b_block_2d, int num_sms, ptb_stream_t stream);
+
+/* Grouped GEMM over row segments of a (forward and dgrad of the MoE experts):
+ *   out[offs[g]:offs[g+1], :] = a[offs[g]:offs[g+1], :] . op(b[g]),   rows >= offs[G] zeroed.
+ *   a [M_total, K]; b [G, N, K] (trans_b = 1) or [G, K, N] (trans_b = 0), contiguous;
+ *   group_offs: device int64 [G+1].  Scales as in ptb_gemm_fp8 with an extra group stride on b
+ *   (blockwise: a_scale is indexed by absolute row; b_scale by (g, n/128, kb)).
+ * Replaces primus_turbo::grouped_gemm_fp8_impl
+ * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:817-859) including its
+ * tail-zeroing launch. */
+int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b, int b_dtype,
+                         int trans_b, void *out, int out_dtype, int64_t ldc,
+                         const int64_t *group_offs, int64_t G, int64_t M_total, int64_t N,
+                         int64_t K, int granularity, const float *a_scale,
+                         int64_t a_scale_stride_m, int64_t a_scale_stride_k, const float *b_scale,
+                         int64_t b_scale_stride_g, int64_t b_scale_stride_n,
+                         int64_t b_scale_stride_k, int num_sms, ptb_stream_t stream);
+
+/* Variable-K grouped GEMM (wgrad): out[g] [OUT_M, OUT_N] = lhs_g^T . rhs_g where the contraction
+ * runs over rows [group_offs[g], group_offs[g+1]) of lhs [rows, OUT_M] and rhs [rows, OUT_N].
+ * PTB_BLOCKWISE: every group length is a multiple of 128 (segment-padded operands), scales are
+ * [rows/128, OUT_M] and [rows/128, OUT_N].  Empty groups produce zeros.
+ * Replaces primus_turbo::grouped_gemm_fp8_variable_k_impl (grouped_gemm_fp8_impl.py:862-901). */
+int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_lhs,
+                                    const void *rhs, int rhs_dtype, int64_t ld_rhs, void *out,
+                                    int out_dtype, const int64_t *group_offs, int64_t G,
+                                    int64_t rows, int64_t OUT_M, int64_t OUT_N, int granularity,
+                                    const float *lhs_scale, const float *rhs_scale, int num_sms,
+                                    ptb_stream_t stream);
+
+/* Every device-side wait in the GEMM kernels is bounded (2 s); a kernel whose wait runs out
+ * records a non-zero code (1 copy producer, 2 MMA issuer, 3 epilogue) and leaves normally.
+ * This call copies that code to *status (a host pointer) and optionally clears it.  It
+ * synchronises with the device.  No counterpart in the reference. */
+int ptb_gemm_status(int *status, int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PTB_H_ */

@@ -1,0 +1,112 @@
+"""ctypes binding of the C ABI declared in ``include/ptb.h``.
+
+The shared library is the only compute backend: if it is missing or fails to load, importing this
+module raises.  There is no fallback path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "_C" / "libptb_b200.so"
+
+# element type codes (include/ptb.h)
+PTB_F32, PTB_F16, PTB_BF16, PTB_E4M3, PTB_E5M2 = 0, 1, 2, 3, 4
+PTB_TENSORWISE, PTB_ROWWISE, PTB_BLOCKWISE = 1, 2, 3
+PTB_TENSORWISE_WS_BYTES = 256
+
+_DTYPE_CODE = {
+    torch.float32: PTB_F32,
+    torch.float16: PTB_F16,
+    torch.bfloat16: PTB_BF16,
+    torch.float8_e4m3fn: PTB_E4M3,
+    torch.float8_e5m2: PTB_E5M2,
+}
+
+_P, _I, _L = c_void_p, c_int, c_int64
+
+# name -> argument types; every function returns int except where noted
+_PROTOS = {
+    "ptb_quant_fp8_tensorwise": [_P, _I, _L, _P, _I, _P, _P, _P],
+    "ptb_quant_fp8_tensorwise_with_scale": [_P, _I, _L, _P, _P, _I, _P, _P],
+    "ptb_quant_fp8_rowwise": [_P, _I, _L, _L, _L, _P, _I, _P, _P, _P],
+    "ptb_quant_fp8_block1d": [_P, _I, _L, _L, _I, _P, _I, _P, _P],
+    "ptb_quant_fp8_block1d_dual": [_P, _I, _L, _L, _P, _P, _P, _P, _I, _P],
+    "ptb_quant_fp8_block2d": [_P, _I, _L, _L, _L, _P, _I, _P, _P],
+    "ptb_quant_fp8_segment_row_col": [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P],
+    "ptb_dequant_fp8_tensorwise": [_P, _I, _L, _P, _P, _I, _P],
+    "ptb_dequant_fp8_rowwise": [_P, _I, _L, _L, _L, _P, _P, _I, _P],
+    "ptb_dequant_fp8_block1d": [_P, _I, _L, _L, _I, _P, _P, _I, _P],
+    "ptb_dequant_fp8_block2d": [_P, _I, _L, _L, _L, _P, _P, _I, _P],
+    "ptb_group_offs": [_P, _L, _P, _P],
+    "ptb_transpose_2d_u8": [_P, _L, _L, _L, _P, _P],
+    "ptb_gemm_fp8": [_P, _I, _I, _L, _P, _I, _I, _L, _P, _I, _L, _L, _L, _L, _I, _P, _L, _L, _P, _L, _L, _I, _I, _P],
+    "ptb_grouped_gemm_fp8": [_P, _I, _L, _P, _I, _I, _P, _I, _L, _P, _L, _L, _L, _L, _I, _P, _L, _L, _P, _L, _L, _L,
+                             _I, _P],
+    "ptb_grouped_gemm_fp8_variable_k": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _I, _P],
+    "ptb_gemm_status": [ctypes.POINTER(c_int), _I],
+}
+
+EXPORTS = ["ptb_version", "ptb_last_error", *_PROTOS.keys()]
+
+
+def _load() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m primus_turbo_b200.build` "
+            "(there is no fallback implementation)"
+        )
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    lib.ptb_version.restype = c_int
+    lib.ptb_version.argtypes = []
+    lib.ptb_last_error.restype = c_char_p
+    lib.ptb_last_error.argtypes = []
+    for name, args in _PROTOS.items():
+        fn = getattr(lib, name)
+        fn.restype = c_int
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+class PtbError(RuntimeError):
+    """A C-ABI call returned a non-zero status (RuntimeError, like the reference's C++ checks)."""
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib.ptb_last_error().decode("utf-8", "replace")
+        raise PtbError(f"{what} failed with status {rc}: {msg}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise PtbError(f"dtype {dt} is not supported by the B200 FP8 library") from None
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise PtbError("tensors must live on a CUDA device: this library has no CPU path")
+
+
+def gemm_status(reset: bool = True) -> int:
+    out = c_int(0)
+    check(lib.ptb_gemm_status(ctypes.byref(out), 1 if reset else 0), "ptb_gemm_status")
+    return out.value

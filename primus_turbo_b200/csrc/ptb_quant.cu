@@ -1,0 +1,706 @@
+// FP8 quantize / dequantize kernels and their C entry points (sm_100a).
+//
+// All of these are HBM-bandwidth bound: every kernel reads its input once with 16-byte loads
+// (twice for the two-pass tensorwise / rowwise reductions, whose second pass is served largely
+// from the 126 MB L2), keeps the tile in registers, reduces the amax with warp shuffles and
+// shared memory, and writes FP8 with 8-byte stores.
+#include "ptb_common.cuh"
+
+namespace ptb {
+
+thread_local char g_err[kErrBufLen] = {0};
+char *err_buf() { return g_err; }
+
+namespace {
+
+constexpr float kEpsTensorRow = 1e-12f; // tensorwise / rowwise floor of the amax
+constexpr float kEpsBlock     = 1e-4f;  // blockwise floor of the amax
+constexpr int kBlk            = 128;    // block size of the blockwise granularities
+
+// ---- 8-element row fragment load / store -----------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load8(const T *__restrict__ row, int64_t col, int64_t ncols, bool vec,
+                                      float (&v)[8]) {
+    if (vec && col + 8 <= ncols) {
+        if constexpr (sizeof(T) == 2) {
+            uint4 raw = *reinterpret_cast<const uint4 *>(row + col);
+            const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = to_f32(e[i]);
+        } else {
+            float4 a = *reinterpret_cast<const float4 *>(row + col);
+            float4 b = *reinterpret_cast<const float4 *>(row + col + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (col + i < ncols) ? to_f32(row[col + i]) : 0.0f;
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ void store8_fp8(uint8_t *__restrict__ row, int64_t col, int64_t ncols, bool vec,
+                                           const float (&v)[8]) {
+    uint16_t p0 = cvt_fp8x2<FMT>(v[0], v[1]);
+    uint16_t p1 = cvt_fp8x2<FMT>(v[2], v[3]);
+    uint16_t p2 = cvt_fp8x2<FMT>(v[4], v[5]);
+    uint16_t p3 = cvt_fp8x2<FMT>(v[6], v[7]);
+    if (vec && col + 8 <= ncols) {
+        uint2 out;
+        out.x = (uint32_t) p0 | ((uint32_t) p1 << 16);
+        out.y = (uint32_t) p2 | ((uint32_t) p3 << 16);
+        *reinterpret_cast<uint2 *>(row + col) = out;
+    } else {
+        uint16_t p[4] = {p0, p1, p2, p3};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (col + i < ncols) row[col + i] = (uint8_t) ((p[i >> 1] >> ((i & 1) * 8)) & 0xff);
+    }
+}
+
+// ---- 128x128 tile quantize: row blocks, column blocks, whole tile, segment-padded ------------
+constexpr int kModeRow = 1; // 1x128 scales
+constexpr int kModeCol = 2; // 128x1 scales
+constexpr int kMode2D  = 4; // one scale per tile
+
+struct BlockQuantArgs {
+    const void *x;
+    uint8_t *q_row;   // row-scaled copy (or the only copy in 2-D mode)
+    uint8_t *q_col;   // column-scaled copy
+    float *s_row;     // [.. m*s_row_stride_m + nb*s_row_stride_nb]
+    float *s_col;     // [mb, N]
+    float *s_2d;      // [b, mb, nb]
+    int64_t B, M, N;
+    int64_t s_row_stride_m, s_row_stride_nb;
+    // segment mode
+    int64_t G;
+    const int64_t *group_offs;
+    int64_t *var_k_lens;
+    int64_t *var_k_offs;
+};
+
+template <typename T, int FMT, int MODE, bool SEGMENT>
+__global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p) {
+    __shared__ float s_colmax[16][kBlk + 1];
+    __shared__ float s_colscale[kBlk];
+    __shared__ float s_red[8];
+    __shared__ int64_t s_seg[4]; // found, orig_start, orig_end, unused
+    __shared__ int64_t s_scan[256];
+
+    const int tid = threadIdx.x;
+    const int tx  = tid & 15;  // 8-column fragment index inside the tile
+    const int ty  = tid >> 4;  // row lane 0..15
+    const int64_t tiles_m = cdiv<int64_t>(SEGMENT ? (p.M + p.G * kBlk) : p.M, kBlk);
+    const int64_t b       = SEGMENT ? 0 : (int64_t) blockIdx.x / tiles_m;
+    const int64_t tm      = SEGMENT ? (int64_t) blockIdx.x : (int64_t) blockIdx.x % tiles_m;
+    const int64_t tn      = blockIdx.y;
+
+    int64_t in_row0  = tm * kBlk; // first source row of this tile
+    int64_t in_end   = p.M;       // first invalid source row
+    const int64_t out_row0 = tm * kBlk;
+
+    if constexpr (SEGMENT) {
+        // Locate the group whose padded segment holds this tile.  Thread t owns a contiguous
+        // chunk of groups; a block-wide scan of the chunk totals gives each chunk's padded start.
+        const int64_t per = cdiv<int64_t>(p.G, 256);
+        const int64_t g0  = (int64_t) tid * per;
+        const int64_t g1  = min(g0 + per, p.G);
+        int64_t local = 0;
+        for (int64_t g = g0; g < g1; ++g) {
+            int64_t len = p.group_offs[g + 1] - p.group_offs[g];
+            local += cdiv<int64_t>(len, kBlk) * kBlk;
+        }
+        s_scan[tid] = local;
+        if (tid == 0) s_seg[0] = 0;
+        __syncthreads();
+        // exclusive prefix over 256 chunk totals (serial in one warp's worth of steps is plenty:
+        // 8 rounds of Hillis-Steele)
+        for (int off = 1; off < 256; off <<= 1) {
+            int64_t add = (tid >= off) ? s_scan[tid - off] : 0;
+            __syncthreads();
+            s_scan[tid] += add;
+            __syncthreads();
+        }
+        int64_t run = s_scan[tid] - local; // padded start of this thread's first group
+        const bool writer = (blockIdx.x == 0 && blockIdx.y == 0);
+        const int64_t block_start = tm * kBlk;
+        for (int64_t g = g0; g < g1; ++g) {
+            int64_t lo = p.group_offs[g], hi = p.group_offs[g + 1];
+            int64_t pl = cdiv<int64_t>(hi - lo, kBlk) * kBlk;
+            if (writer) {
+                p.var_k_lens[g] = pl;
+                p.var_k_offs[g] = run;
+                if (g == p.G - 1) p.var_k_offs[p.G] = run + pl;
+            }
+            if (block_start >= run && block_start < run + pl) {
+                s_seg[0] = 1;
+                s_seg[1] = lo + (block_start - run);
+                s_seg[2] = hi;
+            }
+            run += pl;
+        }
+        if (writer && p.G == 0 && tid == 0) p.var_k_offs[0] = 0;
+        __syncthreads();
+        if (s_seg[0] == 0) return; // tile lies beyond the last padded segment
+        in_row0 = s_seg[1];
+        in_end  = s_seg[2];
+    }
+
+    const T *xb        = reinterpret_cast<const T *>(p.x) + b * p.M * p.N;
+    const int64_t col  = tn * kBlk + tx * 8;
+    const bool vec_in  = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15u) == 0);
+    const bool vec_out = (p.N % 8 == 0);
+
+    float v[8][8];
+    float rmax[8];
+    float cmax[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cmax[j] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t r = in_row0 + ty + 16 * i;
+        if (r < in_end && col < p.N) {
+            load8<T>(xb + r * p.N, col, p.N, vec_in, v[i]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+        }
+        float m = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float a = fabsf(v[i][j]);
+            m       = fmaxf(m, a);
+            cmax[j] = fmaxf(cmax[j], a);
+        }
+        rmax[i] = m;
+    }
+
+    // ---- row blocks: 16 lanes share a row ---------------------------------------------------
+    if constexpr (MODE & kModeRow) {
+        uint8_t *qb = p.q_row + b * p.M * p.N;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float m = rmax[i];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float sc, sci;
+            scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+            const int64_t r = in_row0 + ty + 16 * i;
+            if (r < in_end) {
+                if (col < p.N) {
+                    float qv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], sc);
+                    store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
+                }
+                if (tx == 0) p.s_row[r * p.s_row_stride_m + tn * p.s_row_stride_nb] = sci;
+            }
+        }
+    }
+
+    // ---- column blocks: reduce the 16 row lanes through shared memory -----------------------
+    if constexpr (MODE & kModeCol) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_colmax[ty][tx * 8 + j] = cmax[j];
+        __syncthreads();
+        if (tid < kBlk) {
+            float m = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) m = fmaxf(m, s_colmax[k][tid]);
+            float sc, sci;
+            scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+            s_colscale[tid]  = sc;
+            const int64_t c  = tn * kBlk + tid;
+            if (c < p.N) p.s_col[tm * p.N + c] = sci;
+        }
+        __syncthreads();
+        float cs[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cs[j] = s_colscale[tx * 8 + j];
+        uint8_t *qb = p.q_col; // column copy exists only for 2-D inputs (B == 1)
+        const int64_t out_end = SEGMENT ? (out_row0 + kBlk) : p.M;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t r = out_row0 + ty + 16 * i;
+            if (r < out_end && col < p.N) {
+                float qv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], cs[j]);
+                store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
+            }
+        }
+    }
+
+    // ---- whole tile ---------------------------------------------------------------------------
+    if constexpr (MODE & kMode2D) {
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, rmax[i]);
+        m = warp_max(m);
+        if ((tid & 31) == 0) s_red[tid >> 5] = m;
+        __syncthreads();
+        m = s_red[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+        float sc, sci;
+        scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+        uint8_t *qb = p.q_row + b * p.M * p.N;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t r = in_row0 + ty + 16 * i;
+            if (r < in_end && col < p.N) {
+                float qv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], sc);
+                store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
+            }
+        }
+        if (tid == 0) p.s_2d[(b * tiles_m + tm) * gridDim.y + tn] = sci;
+    }
+}
+
+template <int MODE, bool SEGMENT>
+int launch_block_quant(const BlockQuantArgs &a, int x_dtype, int q_dtype, cudaStream_t st) {
+    const int64_t rows = SEGMENT ? (a.M + a.G * kBlk) : a.M;
+    const int64_t tiles_m = cdiv<int64_t>(rows, kBlk) * (SEGMENT ? 1 : a.B);
+    const int64_t tiles_n = cdiv<int64_t>(a.N, kBlk);
+    if (tiles_m == 0 || tiles_n == 0) return 0;
+    PTB_REQUIRE(tiles_n <= 65535 && tiles_m <= 2147483647LL, PTB_ERR_TOO_LARGE, "tile grid too large");
+    dim3 grid((unsigned) tiles_m, (unsigned) tiles_n);
+    PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
+        (quant_block_kernel<T, FMT, MODE, SEGMENT><<<grid, 256, 0, st>>>(a))));
+    PTB_LAUNCH_CHECK("quant_block_kernel");
+    return 0;
+}
+
+// ---- tensorwise -------------------------------------------------------------------------------
+template <typename T> __global__ void __launch_bounds__(512) amax_kernel(const T *__restrict__ x, int64_t n,
+                                                                          unsigned *amax_bits) {
+    __shared__ float s_red[16];
+    constexpr int V = 16 / sizeof(T); // elements per 16-byte load
+    float m = 0.0f;
+    const int64_t nvec = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) ? n / V : 0;
+    const int64_t gtid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t gsz  = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = gtid; i < nvec; i += gsz) {
+        uint4 raw = reinterpret_cast<const uint4 *>(x)[i];
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int j = 0; j < V; ++j) m = fmaxf(m, fabsf(to_f32(e[j])));
+    }
+    for (int64_t i = nvec * V + gtid; i < n; i += gsz) m = fmaxf(m, fabsf(to_f32(x[i])));
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = (threadIdx.x < (blockDim.x >> 5)) ? s_red[threadIdx.x] : 0.0f;
+        m = warp_max(m);
+        // non-negative floats order like their bit patterns
+        if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(m));
+    }
+}
+
+// SCALE_GIVEN: `src` holds the scale itself; otherwise it holds the amax bits.
+template <typename T, int FMT, bool SCALE_GIVEN>
+__global__ void __launch_bounds__(512) quant_tensorwise_kernel(const T *__restrict__ x, int64_t n,
+                                                                const float *__restrict__ src,
+                                                                uint8_t *__restrict__ q, float *scale_inv) {
+    float sc, sci;
+    if constexpr (SCALE_GIVEN) {
+        sc  = *src;
+        sci = __fdiv_rn(1.0f, sc);
+    } else {
+        scale_from_amax<FMT>(*src, kEpsTensorRow, sc, sci);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_inv = sci;
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
+    const int64_t n8   = vec ? n / 8 : 0;
+    const int64_t gtid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t gsz  = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = gtid; i < n8; i += gsz) {
+        float v[8];
+        load8<T>(x, i * 8, n, true, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = quant_val<FMT>(v[j], sc);
+        store8_fp8<FMT>(q, i * 8, n, true, v);
+    }
+    for (int64_t i = n8 * 8 + gtid; i < n; i += gsz) q[i] = cvt_fp8<FMT>(quant_val<FMT>(to_f32(x[i]), sc));
+}
+
+// ---- rowwise, reduction axis contiguous: one CTA per row, two scans of the row ----------------
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) quant_rowwise_inner_kernel(const T *__restrict__ x, int64_t inner,
+                                                                   uint8_t *__restrict__ q,
+                                                                   float *__restrict__ scale_inv) {
+    __shared__ float s_red[8];
+    const int64_t row = blockIdx.x;
+    const T *xr       = x + row * inner;
+    uint8_t *qr       = q + row * inner;
+    const bool vec    = (inner % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
+    float m = 0.0f;
+    for (int64_t c = (int64_t) threadIdx.x * 8; c < inner; c += 256 * 8) {
+        float v[8];
+        load8<T>(xr, c, inner, vec, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+    float sc, sci;
+    scale_from_amax<FMT>(m, kEpsTensorRow, sc, sci);
+    if (threadIdx.x == 0) scale_inv[row] = sci;
+    for (int64_t c = (int64_t) threadIdx.x * 8; c < inner; c += 256 * 8) {
+        float v[8];
+        load8<T>(xr, c, inner, vec, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = quant_val<FMT>(v[j], sc);
+        store8_fp8<FMT>(qr, c, inner, vec, v);
+    }
+}
+
+// ---- rowwise, reduction axis strided: x [B, M, N], reduce over M ------------------------------
+// CTA = 32 column fragments (256 columns) x 8 row lanes, over a chunk of kColChunk rows.
+constexpr int kColChunk = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(256) col_amax_kernel(const T *__restrict__ x, int64_t M, int64_t N,
+                                                        unsigned *__restrict__ amax_bits) {
+    __shared__ float s_m[8][256 + 1];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t b   = blockIdx.z;
+    const int64_t col = (int64_t) blockIdx.x * 256 + tx * 8;
+    const int64_t r0  = (int64_t) blockIdx.y * kColChunk;
+    const int64_t r1  = min(r0 + kColChunk, M);
+    const T *xb       = x + b * M * N;
+    const bool vec    = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+    float cm[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cm[j] = 0.0f;
+    if (col < N) {
+        for (int64_t r = r0 + ty; r < r1; r += 8) {
+            float v[8];
+            load8<T>(xb + r * N, col, N, vec, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cm[j] = fmaxf(cm[j], fabsf(v[j]));
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_m[ty][tx * 8 + j] = cm[j];
+    __syncthreads();
+    const int64_t c = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (c < N) {
+        float m = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) m = fmaxf(m, s_m[k][threadIdx.x]);
+        atomicMax(amax_bits + b * N + c, __float_as_uint(m));
+    }
+}
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) quant_rowwise_outer_kernel(const T *__restrict__ x, int64_t M, int64_t N,
+                                                                   const float *__restrict__ amax,
+                                                                   uint8_t *__restrict__ q,
+                                                                   float *__restrict__ scale_inv) {
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t b   = blockIdx.z;
+    const int64_t col = (int64_t) blockIdx.x * 256 + tx * 8;
+    if (col >= N) return;
+    const int64_t r0 = (int64_t) blockIdx.y * kColChunk;
+    const int64_t r1 = min(r0 + kColChunk, M);
+    const T *xb      = x + b * M * N;
+    uint8_t *qb      = q + b * M * N;
+    const bool vec   = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
+    float sc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float sci = 0.0f;
+        sc[j]     = 0.0f;
+        if (col + j < N) {
+            scale_from_amax<FMT>(amax[b * N + col + j], kEpsTensorRow, sc[j], sci);
+            if (blockIdx.y == 0 && ty == 0) scale_inv[b * N + col + j] = sci;
+        }
+    }
+    for (int64_t r = r0 + ty; r < r1; r += 8) {
+        float v[8];
+        load8<T>(xb + r * N, col, N, vec, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = quant_val<FMT>(v[j], sc[j]);
+        store8_fp8<FMT>(qb + r * N, col, N, vec, v);
+    }
+}
+
+// ---- dequantize: out = cast(float(q) * scale_inv[...]) ----------------------------------------
+// q viewed as [B, M, N]; scale index = b*sb + (m / bm)*sm + (n / bn)*sn.
+struct DequantIdx {
+    int64_t M, N;
+    int64_t sb, bm, sm, bn, sn;
+};
+
+template <typename TO, int FMT>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ q, int64_t n,
+                                                       const float *__restrict__ scale_inv, DequantIdx ix,
+                                                       TO *__restrict__ out) {
+    const int64_t gtid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t gsz  = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = gtid; i < n; i += gsz) {
+        const int64_t col = i % ix.N;
+        const int64_t rw  = i / ix.N;
+        const int64_t m = rw % ix.M, b = rw / ix.M;
+        const int64_t si = b * ix.sb + (m / ix.bm) * ix.sm + (col / ix.bn) * ix.sn;
+        out[i]           = from_f32<TO>(fp8_to_f32<FMT>(q[i]) * scale_inv[si]);
+    }
+}
+
+int launch_dequant(const void *q, int q_dtype, int64_t n, const float *s, const DequantIdx &ix, void *out,
+                   int out_dtype, cudaStream_t st) {
+    if (n == 0) return 0;
+    PTB_REQUIRE(q && s && out, PTB_ERR_ARG, "dequant: null pointer");
+    PTB_REQUIRE(is_hp(out_dtype) && is_fp8(q_dtype), PTB_ERR_ARG, "dequant: bad dtype");
+    const int blocks = (int) imin(cdiv<int64_t>(n, 256), 148 * 16);
+    PTB_SWITCH_HP(out_dtype, TO, PTB_SWITCH_FP8(q_dtype, FMT,
+        (dequant_kernel<TO, FMT><<<blocks, 256, 0, st>>>((const uint8_t *) q, n, s, ix, (TO *) out))));
+    PTB_LAUNCH_CHECK("dequant_kernel");
+    return 0;
+}
+
+// ---- exclusive prefix sum of group lengths ------------------------------------------------------
+__global__ void __launch_bounds__(256) group_offs_kernel(const int64_t *__restrict__ lens, int64_t G,
+                                                          int64_t *__restrict__ offs) {
+    __shared__ int64_t s_scan[256];
+    const int tid     = threadIdx.x;
+    const int64_t per = cdiv<int64_t>(G, 256);
+    const int64_t g0 = (int64_t) tid * per, g1 = min(g0 + per, G);
+    int64_t local = 0;
+    for (int64_t g = g0; g < g1; ++g) local += lens[g];
+    s_scan[tid] = local;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+        int64_t add = (tid >= off) ? s_scan[tid - off] : 0;
+        __syncthreads();
+        s_scan[tid] += add;
+        __syncthreads();
+    }
+    int64_t run = s_scan[tid] - local;
+    for (int64_t g = g0; g < g1; ++g) {
+        offs[g] = run;
+        run += lens[g];
+    }
+    if (tid == 255) offs[G] = s_scan[255];
+}
+
+// ---- byte transpose [B, M, N] -> [B, N, M] ------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *__restrict__ in, int64_t M, int64_t N,
+                                                            uint8_t *__restrict__ out) {
+    __shared__ uint8_t tile[64][64 + 4];
+    const int64_t b  = blockIdx.z;
+    const int64_t m0 = (int64_t) blockIdx.y * 64, n0 = (int64_t) blockIdx.x * 64;
+    const uint8_t *ib = in + b * M * N;
+    uint8_t *ob       = out + b * M * N;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6; // 64 x 4
+    for (int r = ty; r < 64; r += 4) {
+        int64_t m = m0 + r, n = n0 + tx;
+        tile[r][tx] = (m < M && n < N) ? ib[m * N + n] : (uint8_t) 0;
+    }
+    __syncthreads();
+    for (int r = ty; r < 64; r += 4) {
+        int64_t n = n0 + r, m = m0 + tx;
+        if (n < N && m < M) ob[n * M + m] = tile[tx][r];
+    }
+}
+
+} // namespace
+} // namespace ptb
+
+using namespace ptb;
+
+// =================================================================================================
+// C entry points
+// =================================================================================================
+extern "C" {
+#pragma GCC visibility push(default)
+
+int ptb_version(void) { return PTB_VERSION; }
+const char *ptb_last_error(void) { return err_buf(); }
+
+int ptb_quant_fp8_tensorwise(const void *x, int x_dtype, int64_t n, void *q, int q_dtype, float *scale_inv,
+                             void *workspace, ptb_stream_t stream) {
+    PTB_REQUIRE(n >= 0, PTB_ERR_ARG, "quant_tensorwise: n < 0");
+    PTB_REQUIRE(scale_inv && workspace, PTB_ERR_ARG, "quant_tensorwise: null scale_inv/workspace");
+    PTB_REQUIRE(n == 0 || (x && q), PTB_ERR_ARG, "quant_tensorwise: null x/q");
+    PTB_REQUIRE(is_hp(x_dtype) && is_fp8(q_dtype), PTB_ERR_ARG, "quant_tensorwise: bad dtype");
+    cudaStream_t st = (cudaStream_t) stream;
+    PTB_CUDA(cudaMemsetAsync(workspace, 0, sizeof(unsigned), st));
+    const int blocks = (int) imax(1, imin(cdiv<int64_t>(n, 512 * 8), 148 * 4));
+    if (n > 0) {
+        PTB_SWITCH_HP(x_dtype, T, (amax_kernel<T><<<blocks, 512, 0, st>>>((const T *) x, n, (unsigned *) workspace)));
+        PTB_LAUNCH_CHECK("amax_kernel");
+    }
+    PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
+        (quant_tensorwise_kernel<T, FMT, false><<<blocks, 512, 0, st>>>((const T *) x, n, (const float *) workspace,
+                                                                         (uint8_t *) q, scale_inv))));
+    PTB_LAUNCH_CHECK("quant_tensorwise_kernel");
+    return 0;
+}
+
+int ptb_quant_fp8_tensorwise_with_scale(const void *x, int x_dtype, int64_t n, const float *scale, void *q,
+                                        int q_dtype, float *scale_inv, ptb_stream_t stream) {
+    PTB_REQUIRE(n >= 0 && scale && scale_inv, PTB_ERR_ARG, "quant_tensorwise_with_scale: bad argument");
+    PTB_REQUIRE(n == 0 || (x && q), PTB_ERR_ARG, "quant_tensorwise_with_scale: null x/q");
+    PTB_REQUIRE(is_hp(x_dtype) && is_fp8(q_dtype), PTB_ERR_ARG, "quant_tensorwise_with_scale: bad dtype");
+    cudaStream_t st  = (cudaStream_t) stream;
+    const int blocks = (int) imax(1, imin(cdiv<int64_t>(n, 512 * 8), 148 * 4));
+    PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
+        (quant_tensorwise_kernel<T, FMT, true><<<blocks, 512, 0, st>>>((const T *) x, n, scale, (uint8_t *) q,
+                                                                        scale_inv))));
+    PTB_LAUNCH_CHECK("quant_tensorwise_kernel");
+    return 0;
+}
+
+int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, void *q, int q_dtype,
+                          float *scale_inv, void *workspace, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "quant_rowwise: negative size");
+    PTB_REQUIRE(is_hp(x_dtype) && is_fp8(q_dtype), PTB_ERR_ARG, "quant_rowwise: bad dtype");
+    if (B * N == 0) return 0;
+    PTB_REQUIRE(scale_inv, PTB_ERR_ARG, "quant_rowwise: null scale_inv");
+    PTB_REQUIRE(M == 0 || (x && q), PTB_ERR_ARG, "quant_rowwise: null x/q");
+    cudaStream_t st = (cudaStream_t) stream;
+    if (N == 1) {
+        PTB_REQUIRE(B <= 2147483647LL, PTB_ERR_TOO_LARGE, "quant_rowwise: too many rows");
+        PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
+            (quant_rowwise_inner_kernel<T, FMT><<<(unsigned) B, 256, 0, st>>>((const T *) x, M, (uint8_t *) q,
+                                                                               scale_inv))));
+        PTB_LAUNCH_CHECK("quant_rowwise_inner_kernel");
+        return 0;
+    }
+    PTB_REQUIRE(workspace, PTB_ERR_ARG, "quant_rowwise: null workspace");
+    PTB_REQUIRE(B <= 65535 && cdiv<int64_t>(M, kColChunk) <= 65535, PTB_ERR_TOO_LARGE, "quant_rowwise: grid too large");
+    PTB_CUDA(cudaMemsetAsync(workspace, 0, sizeof(float) * B * N, st));
+    dim3 grid((unsigned) cdiv<int64_t>(N, 256), (unsigned) imax(1, cdiv<int64_t>(M, kColChunk)), (unsigned) B);
+    PTB_SWITCH_HP(x_dtype, T, (col_amax_kernel<T><<<grid, 256, 0, st>>>((const T *) x, M, N, (unsigned *) workspace)));
+    PTB_LAUNCH_CHECK("col_amax_kernel");
+    PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
+        (quant_rowwise_outer_kernel<T, FMT><<<grid, 256, 0, st>>>((const T *) x, M, N, (const float *) workspace,
+                                                                   (uint8_t *) q, scale_inv))));
+    PTB_LAUNCH_CHECK("quant_rowwise_outer_kernel");
+    return 0;
+}
+
+int ptb_quant_fp8_block1d(const void *x, int x_dtype, int64_t M, int64_t N, int axis, void *q, int q_dtype,
+                          float *scale_inv, ptb_stream_t stream) {
+    PTB_REQUIRE(M >= 0 && N >= 0 && (axis == 0 || axis == 1), PTB_ERR_ARG, "quant_block1d: bad size/axis");
+    if (M * N == 0) return 0;
+    PTB_REQUIRE(x && q && scale_inv, PTB_ERR_ARG, "quant_block1d: null pointer");
+    BlockQuantArgs a{};
+    a.x = x; a.B = 1; a.M = M; a.N = N;
+    if (axis == 1) {
+        a.q_row = (uint8_t *) q; a.s_row = scale_inv;
+        a.s_row_stride_m = cdiv<int64_t>(N, kBlk); a.s_row_stride_nb = 1;
+        return launch_block_quant<kModeRow, false>(a, x_dtype, q_dtype, (cudaStream_t) stream);
+    }
+    a.q_col = (uint8_t *) q; a.s_col = scale_inv;
+    return launch_block_quant<kModeCol, false>(a, x_dtype, q_dtype, (cudaStream_t) stream);
+}
+
+int ptb_quant_fp8_block1d_dual(const void *x, int x_dtype, int64_t M, int64_t N, void *q_row, float *s_row,
+                               void *q_col, float *s_col, int q_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(M >= 0 && N >= 0, PTB_ERR_ARG, "quant_block1d_dual: negative size");
+    if (M * N == 0) return 0;
+    PTB_REQUIRE(x && q_row && s_row && q_col && s_col, PTB_ERR_ARG, "quant_block1d_dual: null pointer");
+    BlockQuantArgs a{};
+    a.x = x; a.B = 1; a.M = M; a.N = N;
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row;
+    a.s_row_stride_m = cdiv<int64_t>(N, kBlk); a.s_row_stride_nb = 1;
+    a.q_col = (uint8_t *) q_col; a.s_col = s_col;
+    return launch_block_quant<kModeRow | kModeCol, false>(a, x_dtype, q_dtype, (cudaStream_t) stream);
+}
+
+int ptb_quant_fp8_block2d(const void *w, int w_dtype, int64_t B, int64_t M, int64_t N, void *q, int q_dtype,
+                          float *scale_inv, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "quant_block2d: negative size");
+    if (B * M * N == 0) return 0;
+    PTB_REQUIRE(w && q && scale_inv, PTB_ERR_ARG, "quant_block2d: null pointer");
+    BlockQuantArgs a{};
+    a.x = w; a.B = B; a.M = M; a.N = N;
+    a.q_row = (uint8_t *) q; a.s_2d = scale_inv;
+    return launch_block_quant<kMode2D, false>(a, w_dtype, q_dtype, (cudaStream_t) stream);
+}
+
+int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t N, int64_t G,
+                                  const int64_t *group_lens, const int64_t *group_offs, void *q_row,
+                                  void *q_col_padded, float *s_row, float *s_col_padded, int64_t *var_k_lens,
+                                  int64_t *var_k_offs, int q_dtype, ptb_stream_t stream) {
+    (void) group_lens; // lengths are implied by the offsets
+    PTB_REQUIRE(M >= 0 && N >= 0 && G >= 0, PTB_ERR_ARG, "quant_segment_row_col: negative size");
+    PTB_REQUIRE(group_offs && var_k_lens && var_k_offs, PTB_ERR_ARG, "quant_segment_row_col: null group arrays");
+    PTB_REQUIRE(N > 0, PTB_ERR_ARG, "quant_segment_row_col: N must be positive");
+    PTB_REQUIRE(x && q_row && q_col_padded && s_row && s_col_padded, PTB_ERR_ARG,
+                "quant_segment_row_col: null pointer");
+    BlockQuantArgs a{};
+    a.x = x; a.B = 1; a.M = M; a.N = N; a.G = G;
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row;
+    a.s_row_stride_m = 1; a.s_row_stride_nb = M; // row scales stored [ceil(N/128), M]
+    a.q_col = (uint8_t *) q_col_padded; a.s_col = s_col_padded;
+    a.group_offs = group_offs; a.var_k_lens = var_k_lens; a.var_k_offs = var_k_offs;
+    return launch_block_quant<kModeRow | kModeCol, true>(a, x_dtype, q_dtype, (cudaStream_t) stream);
+}
+
+int ptb_dequant_fp8_tensorwise(const void *q, int q_dtype, int64_t n, const float *scale_inv, void *out,
+                               int out_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(n >= 0, PTB_ERR_ARG, "dequant_tensorwise: n < 0");
+    DequantIdx ix{1, n > 0 ? n : 1, 0, 1, 0, INT64_MAX, 0};
+    return launch_dequant(q, q_dtype, n, scale_inv, ix, out, out_dtype, (cudaStream_t) stream);
+}
+
+int ptb_dequant_fp8_rowwise(const void *q, int q_dtype, int64_t B, int64_t M, int64_t N, const float *scale_inv,
+                            void *out, int out_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "dequant_rowwise: negative size");
+    if (B * M * N == 0) return 0;
+    DequantIdx ix{M, N, N, INT64_MAX, 0, 1, 1}; // scale[b, 0, n]
+    return launch_dequant(q, q_dtype, B * M * N, scale_inv, ix, out, out_dtype, (cudaStream_t) stream);
+}
+
+int ptb_dequant_fp8_block1d(const void *q, int q_dtype, int64_t M, int64_t N, int axis, const float *scale_inv,
+                            void *out, int out_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(M >= 0 && N >= 0 && (axis == 0 || axis == 1), PTB_ERR_ARG, "dequant_block1d: bad size/axis");
+    if (M * N == 0) return 0;
+    DequantIdx ix = (axis == 1) ? DequantIdx{M, N, 0, 1, cdiv<int64_t>(N, kBlk), kBlk, 1}  // scale[m, n/128]
+                                : DequantIdx{M, N, 0, kBlk, N, 1, 1};                        // scale[m/128, n]
+    return launch_dequant(q, q_dtype, M * N, scale_inv, ix, out, out_dtype, (cudaStream_t) stream);
+}
+
+int ptb_dequant_fp8_block2d(const void *q, int q_dtype, int64_t B, int64_t M, int64_t N, const float *scale_inv,
+                            void *out, int out_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "dequant_block2d: negative size");
+    if (B * M * N == 0) return 0;
+    const int64_t mb = cdiv<int64_t>(M, kBlk), nb = cdiv<int64_t>(N, kBlk);
+    DequantIdx ix{M, N, mb * nb, kBlk, nb, kBlk, 1}; // scale[b, m/128, n/128]
+    return launch_dequant(q, q_dtype, B * M * N, scale_inv, ix, out, out_dtype, (cudaStream_t) stream);
+}
+
+int ptb_group_offs(const int64_t *group_lens, int64_t G, int64_t *group_offs, ptb_stream_t stream) {
+    PTB_REQUIRE(G >= 0 && group_offs && (G == 0 || group_lens), PTB_ERR_ARG, "group_offs: bad argument");
+    group_offs_kernel<<<1, 256, 0, (cudaStream_t) stream>>>(group_lens, G, group_offs);
+    PTB_LAUNCH_CHECK("group_offs_kernel");
+    return 0;
+}
+
+int ptb_transpose_2d_u8(const void *in, int64_t B, int64_t M, int64_t N, void *out, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "transpose_2d_u8: negative size");
+    if (B * M * N == 0) return 0;
+    PTB_REQUIRE(in && out, PTB_ERR_ARG, "transpose_2d_u8: null pointer");
+    PTB_REQUIRE(B <= 65535 && cdiv<int64_t>(M, 64) <= 65535, PTB_ERR_TOO_LARGE, "transpose_2d_u8: grid too large");
+    dim3 grid((unsigned) cdiv<int64_t>(N, 64), (unsigned) cdiv<int64_t>(M, 64), (unsigned) B);
+    transpose_u8_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) in, M, N, (uint8_t *) out);
+    PTB_LAUNCH_CHECK("transpose_u8_kernel");
+    return 0;
+}
+
+#pragma GCC visibility pop
+} // extern "C"

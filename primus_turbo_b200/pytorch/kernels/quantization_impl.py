@@ -1,0 +1,285 @@
+"""Thin torch layer over the quantize / dequantize entry points of the C ABI.
+
+Each function allocates its outputs with torch on the input's device and passes raw pointers and
+the current CUDA stream to the library, the way the reference's C++ bindings allocate with
+``at::empty`` and enqueue on the current stream (csrc/pytorch/quantization/quantization.cpp:48,77).
+Function names and return conventions follow
+primus_turbo/pytorch/kernels/quantization/quantization_impl.py.
+"""
+
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from primus_turbo_b200 import _lib
+from primus_turbo_b200._lib import check, dtype_code, lib, ptr, require_cuda, stream_of
+
+
+def ceil_div(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+def _check_in(x: torch.Tensor, allow_fp32: bool = True) -> None:
+    require_cuda(x)
+    ok = (torch.float16, torch.bfloat16, torch.float32) if allow_fp32 else (torch.float16, torch.bfloat16)
+    if x.dtype not in ok:
+        raise _lib.PtbError(f"input dtype {x.dtype} is not supported")
+
+
+def quantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scale: torch.Tensor | None = None):
+    """quantization.cpp:42-88: returns (x_fp8, scale_inv[]) ."""
+    _check_in(x)
+    xc = x.contiguous()
+    q = torch.empty(xc.shape, dtype=out_dtype, device=x.device)
+    scale_inv = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        if scale is None:
+            ws = torch.empty(_lib.PTB_TENSORWISE_WS_BYTES, dtype=torch.uint8, device=x.device)
+            check(
+                lib.ptb_quant_fp8_tensorwise(
+                    ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(q), dtype_code(out_dtype), ptr(scale_inv), ptr(ws),
+                    stream_of(x),
+                ),
+                "ptb_quant_fp8_tensorwise",
+            )
+        else:
+            assert scale.numel() == 1, "tensorwise scale must be scalar tensor"
+            sc = scale.to(device=x.device, dtype=torch.float32).contiguous()
+            check(
+                lib.ptb_quant_fp8_tensorwise_with_scale(
+                    ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(sc), ptr(q), dtype_code(out_dtype), ptr(scale_inv),
+                    stream_of(x),
+                ),
+                "ptb_quant_fp8_tensorwise_with_scale",
+            )
+    return q, scale_inv
+
+
+def _bmn(shape, axis: int) -> Tuple[int, int, int]:
+    B = 1
+    for d in shape[:axis]:
+        B *= d
+    N = 1
+    for d in shape[axis + 1 :]:
+        N *= d
+    return B, shape[axis], N
+
+
+def quantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int):
+    """quantization.cpp:108-206: scale_inv keeps x's shape with shape[axis] = 1."""
+    _check_in(x)
+    assert x.is_contiguous(), "The x tensor must be contiguous."
+    nd = x.dim()
+    ax = axis if axis >= 0 else nd + axis
+    if not (0 <= ax < nd):
+        raise _lib.PtbError(f"axis {axis} out of range for a {nd}-d tensor")
+    B, M, N = _bmn(tuple(x.shape), ax)
+    sshape = list(x.shape)
+    sshape[ax] = 1
+    q = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    scale_inv = torch.empty(sshape, dtype=torch.float32, device=x.device)
+    ws = torch.empty(max(B * N, 1), dtype=torch.float32, device=x.device) if N > 1 else None
+    with torch.cuda.device(x.device):
+        check(
+            lib.ptb_quant_fp8_rowwise(
+                ptr(x), dtype_code(x.dtype), B, M, N, ptr(q), dtype_code(out_dtype), ptr(scale_inv), ptr(ws),
+                stream_of(x),
+            ),
+            "ptb_quant_fp8_rowwise",
+        )
+    return q, scale_inv
+
+
+def quant_fp8_blockwise_impl(x: torch.Tensor, dtype: torch.dtype, axis: int, block_size: int = 128):
+    """quantization_impl.py:74-118."""
+    assert x.is_contiguous() and x.dim() == 2, "Input must be 2D and contiguous"
+    assert axis in (-2, -1, 0, 1), f"axis must be 0 or 1 (or -1, -2), got {axis}"
+    assert block_size == 128, "Only block_size 128 is supported"
+    _check_in(x)
+    axis = axis % 2
+    M, N = x.shape
+    q = torch.empty((M, N), dtype=dtype, device=x.device)
+    sshape = (M, ceil_div(N, block_size)) if axis == 1 else (ceil_div(M, block_size), N)
+    s = torch.empty(sshape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib.ptb_quant_fp8_block1d(
+                ptr(x), dtype_code(x.dtype), M, N, axis, ptr(q), dtype_code(dtype), ptr(s), stream_of(x)
+            ),
+            "ptb_quant_fp8_block1d",
+        )
+    return q, s
+
+
+def quant_fp8_blockwise_dual_impl(x: torch.Tensor, dtype: torch.dtype, block_size: int = 128):
+    """quantization_impl.py:229-274: (row copy, row scales [M, N/128], col copy, col scales [M/128, N])."""
+    assert x.is_contiguous() and x.dim() == 2, "Input must be 2D and contiguous"
+    assert block_size == 128, "Only block_size 128 is supported"
+    _check_in(x)
+    M, N = x.shape
+    q_row = torch.empty((M, N), dtype=dtype, device=x.device)
+    s_row = torch.empty((M, ceil_div(N, block_size)), dtype=torch.float32, device=x.device)
+    q_col = torch.empty((M, N), dtype=dtype, device=x.device)
+    s_col = torch.empty((ceil_div(M, block_size), N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib.ptb_quant_fp8_block1d_dual(
+                ptr(x), dtype_code(x.dtype), M, N, ptr(q_row), ptr(s_row), ptr(q_col), ptr(s_col), dtype_code(dtype),
+                stream_of(x),
+            ),
+            "ptb_quant_fp8_block1d_dual",
+        )
+    return q_row, s_row, q_col, s_col
+
+
+def quant_fp8_blockwise_for_weight_impl(w: torch.Tensor, dtype: torch.dtype, block_size: int = 128):
+    """quantization_impl.py:295-350: 2-D or 3-D weight, one scale per 128x128 tile."""
+    assert w.dim() in (2, 3)
+    assert block_size == 128, "Only block_size 128 is supported"
+    _check_in(w)
+    if not w.is_contiguous():
+        w = w.contiguous()
+    if w.dim() == 2:
+        B, (M, N) = 1, w.shape
+        sshape = (ceil_div(M, block_size), ceil_div(N, block_size))
+    else:
+        B, M, N = w.shape
+        sshape = (B, ceil_div(M, block_size), ceil_div(N, block_size))
+    q = torch.empty(w.shape, dtype=dtype, device=w.device)
+    s = torch.empty(sshape, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(
+            lib.ptb_quant_fp8_block2d(
+                ptr(w), dtype_code(w.dtype), B, M, N, ptr(q), dtype_code(dtype), ptr(s), stream_of(w)
+            ),
+            "ptb_quant_fp8_block2d",
+        )
+    return q, s
+
+
+def quant_fp8_blockwise_segment_m_row_col_impl(
+    x: torch.Tensor,
+    dtype: torch.dtype,
+    block_size: int,
+    group_lens: torch.Tensor,
+    group_offs: torch.Tensor,
+    gemm_other_dim: int | None = None,
+):
+    """quantization_impl.py:379-464.  Returns (x_fp8_row [M,N], x_fp8_col_padded [M+128G,N],
+    x_scales_row [N/128, M], x_scales_col_padded [(M+128G)/128, N], var_k_group_lens [G],
+    var_k_group_offs [G+1])."""
+    assert x.is_contiguous() and x.dim() == 2
+    assert block_size == 128, "Only block_size 128 is supported"
+    _check_in(x)
+    require_cuda(group_lens, group_offs)
+    assert group_lens.dtype == torch.int64 and group_offs.dtype == torch.int64
+    M, N = x.shape
+    G = group_lens.numel()
+    m_pad = M + G * block_size
+    dev = x.device
+    q_row = torch.empty((M, N), dtype=dtype, device=dev)
+    q_col = torch.empty((m_pad, N), dtype=dtype, device=dev)
+    s_row = torch.empty((ceil_div(N, block_size), M), dtype=torch.float32, device=dev)
+    s_col = torch.empty((ceil_div(m_pad, block_size), N), dtype=torch.float32, device=dev)
+    vk_lens = torch.empty(G, dtype=torch.int64, device=dev)
+    vk_offs = torch.empty(G + 1, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(
+            lib.ptb_quant_fp8_segment_row_col(
+                ptr(x), dtype_code(x.dtype), M, N, G, ptr(group_lens.contiguous()), ptr(group_offs.contiguous()),
+                ptr(q_row), ptr(q_col), ptr(s_row), ptr(s_col), ptr(vk_lens), ptr(vk_offs), dtype_code(dtype),
+                stream_of(x),
+            ),
+            "ptb_quant_fp8_segment_row_col",
+        )
+    return q_row, q_col, s_row, s_col, vk_lens, vk_offs
+
+
+# ---- dequantize ------------------------------------------------------------------------------------
+def dequantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scale_inv: torch.Tensor):
+    require_cuda(x, scale_inv)
+    xc = x.contiguous()
+    out = torch.empty(xc.shape, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib.ptb_dequant_fp8_tensorwise(
+                ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(scale_inv.contiguous()), ptr(out),
+                dtype_code(out_dtype), stream_of(x),
+            ),
+            "ptb_dequant_fp8_tensorwise",
+        )
+    return out
+
+
+def dequantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int, scale_inv: torch.Tensor):
+    assert x.is_contiguous(), "The x tensor must be contiguous."
+    assert scale_inv.is_contiguous(), "The scale_inv tensor must be contiguous."
+    require_cuda(x, scale_inv)
+    nd = x.dim()
+    ax = axis if axis >= 0 else nd + axis
+    B, M, N = _bmn(tuple(x.shape), ax)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib.ptb_dequant_fp8_rowwise(
+                ptr(x), dtype_code(x.dtype), B, M, N, ptr(scale_inv), ptr(out), dtype_code(out_dtype), stream_of(x)
+            ),
+            "ptb_dequant_fp8_rowwise",
+        )
+    return out
+
+
+def dequant_fp8_blockwise_impl(x_fp8, scale_inv, out_dtype, axis: int, block_size: int = 128):
+    assert x_fp8.is_contiguous() and x_fp8.dim() == 2, "Input must be 2D and contiguous"
+    assert axis in (-2, -1, 0, 1), f"axis must be 0 or 1 (or -1, -2), got {axis}"
+    assert block_size == 128
+    require_cuda(x_fp8, scale_inv)
+    axis = axis % 2
+    M, N = x_fp8.shape
+    out = torch.empty((M, N), dtype=out_dtype, device=x_fp8.device)
+    with torch.cuda.device(x_fp8.device):
+        check(
+            lib.ptb_dequant_fp8_block1d(
+                ptr(x_fp8), dtype_code(x_fp8.dtype), M, N, axis, ptr(scale_inv.contiguous()), ptr(out),
+                dtype_code(out_dtype), stream_of(x_fp8),
+            ),
+            "ptb_dequant_fp8_block1d",
+        )
+    return out
+
+
+def dequant_fp8_blockwise_for_weight_impl(w_fp8, scale_inv, out_dtype, block_size: int = 128):
+    assert w_fp8.dim() in (2, 3)
+    assert block_size == 128
+    require_cuda(w_fp8, scale_inv)
+    if not w_fp8.is_contiguous():
+        w_fp8 = w_fp8.contiguous()
+    if w_fp8.dim() == 2:
+        B, (M, N) = 1, w_fp8.shape
+    else:
+        B, M, N = w_fp8.shape
+    out = torch.empty(w_fp8.shape, dtype=out_dtype, device=w_fp8.device)
+    with torch.cuda.device(w_fp8.device):
+        check(
+            lib.ptb_dequant_fp8_block2d(
+                ptr(w_fp8), dtype_code(w_fp8.dtype), B, M, N, ptr(scale_inv.contiguous()), ptr(out),
+                dtype_code(out_dtype), stream_of(w_fp8),
+            ),
+            "ptb_dequant_fp8_block2d",
+        )
+    return out
+
+
+def transpose_2d_fp8(x: torch.Tensor) -> torch.Tensor:
+    """[..., M, N] -> [..., N, M] physical transpose of an FP8 payload (reference op transpose_2d)."""
+    require_cuda(x)
+    assert x.dim() >= 2 and x.element_size() == 1
+    xc = x.contiguous()
+    M, N = xc.shape[-2:]
+    B = xc.numel() // max(M * N, 1) if M * N else 0
+    out = torch.empty((*xc.shape[:-2], N, M), dtype=xc.dtype, device=xc.device)
+    with torch.cuda.device(x.device):
+        check(lib.ptb_transpose_2d_u8(ptr(xc), B, M, N, ptr(out), stream_of(x)), "ptb_transpose_2d_u8")
+    return out
