@@ -170,8 +170,11 @@ int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b,
 
 /* Variable-K grouped GEMM (wgrad): out[g] [OUT_M, OUT_N] = lhs_g^T . rhs_g where the contraction
  * runs over rows [group_offs[g], group_offs[g+1]) of lhs [rows, OUT_M] and rhs [rows, OUT_N].
- * PTB_BLOCKWISE: every group length is a multiple of 128 (segment-padded operands), scales are
- * [rows/128, OUT_M] and [rows/128, OUT_N].  Empty groups produce zeros.
+ * Empty groups produce zeros.
+ *   PTB_BLOCKWISE:  every group offset is a multiple of 128 (segment-padded operands); scales are
+ *                   [rows/128, OUT_M] and [rows/128, OUT_N], applied per 128-row block.
+ *   PTB_ROWWISE:    lhs_scale[OUT_M], rhs_scale[OUT_N] applied to the finished tile; any offsets.
+ *   PTB_TENSORWISE: lhs_scale[1], rhs_scale[1]; any offsets.
  * Replaces primus_turbo::grouped_gemm_fp8_variable_k_impl (grouped_gemm_fp8_impl.py:862-901). */
 int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_lhs,
                                     const void *rhs, int rhs_dtype, int64_t ld_rhs, void *out,

@@ -85,6 +85,48 @@ def check(rc: int, what: str) -> None:
         raise PtbError(f"{what} failed with status {rc}: {msg}")
 
 
+# kernels enqueued by one successful call of each entry point (memset nodes not counted)
+KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_gemm_status": 0}
+launch_count = 0  # running total of kernels this process enqueued through the C ABI
+_event_log = None  # when a dict: name -> [(start_event, stop_event), ...] on the launching stream
+
+
+def call(name: str, *args) -> None:
+    """Invoke one C-ABI entry point: count its launches, optionally bracket it with CUDA events on
+    the current stream (see record_kernel_times), raise PtbError on a non-zero status."""
+    global launch_count
+    fn = getattr(lib, name)
+    if _event_log is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(*args)
+        e1.record()
+        _event_log.setdefault(name, []).append((e0, e1))
+    else:
+        rc = fn(*args)
+    check(rc, name)
+    launch_count += KERNELS_PER_CALL.get(name, 1)
+
+
+class record_kernel_times:
+    """Context manager: per-entry-point device durations (ms) of every call made inside it."""
+
+    def __enter__(self):
+        global _event_log
+        self._prev, _event_log = _event_log, {}
+        self.log = _event_log
+        return self
+
+    def __exit__(self, *exc):
+        global _event_log
+        _event_log = self._prev
+        return False
+
+    def durations_ms(self):
+        torch.cuda.synchronize()
+        return {k: [a.elapsed_time(b) for a, b in v] for k, v in self.log.items()}
+
+
 def dtype_code(dt: torch.dtype) -> int:
     try:
         return _DTYPE_CODE[dt]

@@ -149,6 +149,7 @@ struct Tile {
     int g;         // group (0 for dense)
     int k_row0;    // first contraction row (variable-K) else 0
     int num_kb;    // 128-wide contraction blocks
+    int k_tail;    // variable-K only: valid rows of the last block when the group length is not a multiple of 128, else 0
 };
 
 struct Schedule {
@@ -173,7 +174,7 @@ struct Schedule {
             const int r       = t - gi * band;
             const int mt = first + r % rows, nt = r / rows;
             o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * BN; o.g = 0; o.k_row0 = 0;
-            o.num_kb = (a.K + BK - 1) / BK;
+            o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
         } else if (a.kind == kKindGroupedRows) {
             const int mbi = t / a.tiles_n, nt = t - mbi * a.tiles_n;
             while (tile_prefix[cursor_g + 1] <= mbi) ++cursor_g;
@@ -181,7 +182,7 @@ struct Schedule {
             const int64_t lo   = a.group_offs[g];
             const int64_t hi   = a.group_offs[g + 1];
             o.m0 = (int) lo + (mbi - tile_prefix[g]) * BM; o.m_end = (int) hi; o.n0 = nt * BN; o.g = g;
-            o.k_row0 = 0; o.num_kb = (a.K + BK - 1) / BK;
+            o.k_row0 = 0; o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
         } else {
             const int tiles_m = (a.M + BM - 1) / BM;
             const int per_g   = tiles_m * a.tiles_n;
@@ -190,6 +191,7 @@ struct Schedule {
             const int64_t lo = a.group_offs[g], hi = a.group_offs[g + 1];
             o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * BN; o.g = g; o.k_row0 = (int) lo;
             o.num_kb = (int) ((hi - lo + BK - 1) / BK);
+            o.k_tail = (int) ((hi - lo) % BK);
         }
         return true;
     }
@@ -335,8 +337,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                     mbar_wait(smem_u32(&ctl->full[q % kStages]), (q / kStages) & 1);
                 }
             }
-        } else if (warp == 1 && lane == 0) {
-            // ================= MMA issuer =================
+        } else if (warp == 1) {
+            // ================= MMA issuer (whole warp walks the schedule, lane 0 issues) =================
             Schedule sched(args, ctl->tile_prefix, total_tiles);
             Tile t;
             uint32_t it = 0, acc_it = 0;
@@ -354,26 +356,37 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                         if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), ((acc_it >> 1) & 1) ^ 1)) { ok = false; break; }
                     }
                     if (!mbar_wait(smem_u32(&ctl->full[s]), ph)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kABytes;
-                    const uint64_t ad = make_smem_desc(sa, a_lbo, a_sbo);
-                    const uint64_t bd = make_smem_desc(sb, b_lbo, b_sbo);
-                    const uint32_t d  = tmem_base + buf * BN;
-#pragma unroll
-                    for (int j = 0; j < BK / 32; ++j) {
-                        const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
-                        tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
-                                  args.idesc, accumulate);
+                    uint8_t *a_tile = smem + s * kStageBytes;
+                    if (t.k_tail != 0 && kb == t.num_kb - 1) {
+                        // The last block of an unpadded group reaches into the next group's rows:
+                        // clear those contraction rows of the (MN-major) A tile so they add nothing.
+                        for (int off = t.k_tail * 128 + lane * 16; off < kABytes; off += 32 * 16)
+                            *reinterpret_cast<uint4 *>(a_tile + off) = make_uint4(0, 0, 0, 0);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     }
-                    tc_commit(smem_u32(&ctl->empty[s])); // stage reusable once these MMAs retire
+                    __syncwarp();
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kABytes;
+                        const uint64_t ad = make_smem_desc(sa, a_lbo, a_sbo);
+                        const uint64_t bd = make_smem_desc(sb, b_lbo, b_sbo);
+                        const uint32_t d  = tmem_base + buf * BN;
+#pragma unroll
+                        for (int j = 0; j < BK / 32; ++j) {
+                            const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
+                            tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
+                                      args.idesc, accumulate);
+                        }
+                        tc_commit(smem_u32(&ctl->empty[s])); // stage reusable once these MMAs retire
+                    }
                     const bool last = kPerBlock || kb == t.num_kb - 1;
                     if (last) {
-                        tc_commit(smem_u32(&ctl->tmem_full[buf]));
+                        if (lane == 0) tc_commit(smem_u32(&ctl->tmem_full[buf]));
                         ++acc_it;
                     }
                 }
             }
-            if (!ok) atomicExch(&g_gemm_status, 2);
+            if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -686,8 +699,9 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
                                     ptb_stream_t stream) {
     PTB_REQUIRE(G >= 0 && rows >= 0 && OUT_M >= 0 && OUT_N >= 0, PTB_ERR_ARG, "grouped_gemm_fp8_variable_k: bad shape");
     if (G == 0 || OUT_M == 0 || OUT_N == 0) return 0;
-    PTB_REQUIRE(granularity == PTB_BLOCKWISE, PTB_ERR_UNSUPPORTED,
-                "grouped_gemm_fp8_variable_k: only blockwise scaling over segment-padded rows is implemented");
+    int mode;
+    int rc = scale_mode_of(granularity, 0, &mode);
+    if (rc) return rc;
     PTB_REQUIRE(lhs && rhs && out && group_offs && lhs_scale && rhs_scale, PTB_ERR_ARG,
                 "grouped_gemm_fp8_variable_k: null pointer");
     PTB_REQUIRE(is_fp8(lhs_dtype) && is_fp8(rhs_dtype), PTB_ERR_ARG, "grouped_gemm_fp8_variable_k: operands must be FP8");
@@ -696,7 +710,7 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
                 PTB_ERR_TOO_LARGE, "grouped_gemm_fp8_variable_k: problem too large");
     GemmArgs g{};
     const uint64_t r = rows > 0 ? (uint64_t) rows : 1;
-    int rc = make_map(&g.tm_a, lhs, (uint64_t) OUT_M, r, 1, (uint64_t) ld_lhs, (uint64_t) ld_lhs * r, BK);
+    rc = make_map(&g.tm_a, lhs, (uint64_t) OUT_M, r, 1, (uint64_t) ld_lhs, (uint64_t) ld_lhs * r, BK);
     if (rc) return rc;
     rc = make_map(&g.tm_b, rhs, (uint64_t) OUT_N, r, 1, (uint64_t) ld_rhs, (uint64_t) ld_rhs * r, BK);
     if (rc) return rc;
@@ -708,7 +722,7 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
     g.c = out; g.ldc = OUT_N; g.c_group_stride = OUT_M * OUT_N;
     g.a_scale = lhs_scale; g.as_m = 1; g.as_k = OUT_M;
     g.b_scale = rhs_scale; g.bs_g = 0; g.bs_n = 1; g.bs_k = OUT_N;
-    return launch_gemm(g, kScaleBlock1D, out_dtype, num_sms, (cudaStream_t) stream);
+    return launch_gemm(g, mode, out_dtype, num_sms, (cudaStream_t) stream);
 }
 
 #pragma GCC visibility pop

@@ -98,14 +98,9 @@ def gemm_fp8_impl(
     else:
         raise ValueError(f"Unsupported granularity {granularity}")
     with torch.cuda.device(a.device):
-        check(
-            lib.ptb_gemm_fp8(
-                ptr(a), dtype_code(a.dtype), int(trans_a), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b),
+        _lib.call("ptb_gemm_fp8", ptr(a), dtype_code(a.dtype), int(trans_a), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b),
                 b.stride(0), ptr(out), dtype_code(out_dtype), out.stride(0), m, n, k, granularity, ptr(a_s), asm, ask,
-                ptr(b_s), bsn, bsk, b_block_2d, num_sms, stream_of(a),
-            ),
-            "ptb_gemm_fp8",
-        )
+                ptr(b_s), bsn, bsk, b_block_2d, num_sms, stream_of(a))
     return out
 
 
@@ -116,7 +111,7 @@ def group_offs_from_lens(group_lens: torch.Tensor) -> torch.Tensor:
     gl = group_lens.contiguous()
     offs = torch.empty(gl.numel() + 1, dtype=torch.int64, device=gl.device)
     with torch.cuda.device(gl.device):
-        check(lib.ptb_group_offs(ptr(gl), gl.numel(), ptr(offs), stream_of(gl)), "ptb_group_offs")
+        _lib.call("ptb_group_offs", ptr(gl), gl.numel(), ptr(offs), stream_of(gl))
     return offs
 
 
@@ -161,14 +156,9 @@ def grouped_gemm_fp8_impl(
     else:
         raise ValueError(f"Unsupported granularity {granularity}")
     with torch.cuda.device(a.device):
-        check(
-            lib.ptb_grouped_gemm_fp8(
-                ptr(a), dtype_code(a.dtype), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b), ptr(out),
+        _lib.call("ptb_grouped_gemm_fp8", ptr(a), dtype_code(a.dtype), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b), ptr(out),
                 dtype_code(out_dtype), out.stride(0), ptr(group_offs.contiguous()), G, m_total, n, k, granularity,
-                ptr(a_s), asm, ask, ptr(b_s), bsg, bsn, bsk, int(num_cu or 0), stream_of(a),
-            ),
-            "ptb_grouped_gemm_fp8",
-        )
+                ptr(a_s), asm, ask, ptr(b_s), bsg, bsn, bsk, int(num_cu or 0), stream_of(a))
     return out
 
 
@@ -198,15 +188,14 @@ def grouped_gemm_fp8_variable_k_impl(
     out_n = rhs.shape[1]
     out = torch.empty((G, out_m, out_n), dtype=out_dtype, device=lhs.device)
     lhs_s, rhs_s = _f32(lhs_s).contiguous(), _f32(rhs_s).contiguous()
+    if granularity == PTB_ROWWISE:
+        assert lhs_s.numel() == out_m and rhs_s.numel() == out_n, "rowwise scales must span the output rows / columns"
+    elif granularity == PTB_TENSORWISE:
+        assert lhs_s.numel() == 1 and rhs_s.numel() == 1
     with torch.cuda.device(lhs.device):
-        check(
-            lib.ptb_grouped_gemm_fp8_variable_k(
-                ptr(lhs), dtype_code(lhs.dtype), lhs.stride(0), ptr(rhs), dtype_code(rhs.dtype), rhs.stride(0),
+        _lib.call("ptb_grouped_gemm_fp8_variable_k", ptr(lhs), dtype_code(lhs.dtype), lhs.stride(0), ptr(rhs), dtype_code(rhs.dtype), rhs.stride(0),
                 ptr(out), dtype_code(out_dtype), ptr(group_offs.contiguous()), G, rows, out_m, out_n, granularity,
-                ptr(lhs_s), ptr(rhs_s), int(num_cu or 0), stream_of(lhs),
-            ),
-            "ptb_grouped_gemm_fp8_variable_k",
-        )
+                ptr(lhs_s), ptr(rhs_s), int(num_cu or 0), stream_of(lhs))
     return out
 
 

@@ -1,0 +1,234 @@
+"""``grouped_gemm_fp8``: MoE grouped GEMM with FP8 quantisation and autograd
+(primus_turbo/pytorch/ops/grouped_gemm_fp8.py:75-211 blockwise, :214-393 rowwise, :396-568
+tensorwise, :808-904 public entry).
+
+``a`` is the packed activation ``[sum(group_lens), K]``; ``b`` is ``[G, N, K]`` (``trans_b``) or
+``[G, K, N]``.  Forward and dgrad run the row-segmented grouped kernel; wgrad runs the variable-K
+kernel whose contraction axis is the group's row range.  Nothing here synchronises with the host:
+group boundaries are read on the device.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+
+from primus_turbo_b200.pytorch.core.low_precision import (
+    Float8QuantConfig,
+    Format,
+    ScalingGranularity,
+    float8_e4m3,
+    float8_e5m2,
+)
+from primus_turbo_b200.pytorch.core.quantized_tensor import (
+    QuantizedTensor,
+    QuantizedTensorPair,
+    check_quantized_tensor,
+)
+from primus_turbo_b200.pytorch.kernels.gemm_impl import (
+    group_offs_from_lens,
+    grouped_gemm_fp8_impl,
+    grouped_gemm_fp8_variable_k_impl,
+)
+from primus_turbo_b200.pytorch.kernels.quantization_impl import (
+    quant_fp8_blockwise_for_weight_impl,
+    quant_fp8_blockwise_segment_m_row_col_impl,
+)
+
+__all__ = ["grouped_gemm_fp8"]
+
+
+def _get_fp8_dtype(format: Format, is_fwd_stage: bool):
+    if format == Format.E4M3:
+        return float8_e4m3
+    if format == Format.E5M2:
+        return float8_e5m2
+    if format == Format.HYBRID:
+        return float8_e4m3 if is_fwd_stage else float8_e5m2
+    raise ValueError(f"Unsupported FP8 format: {format}")
+
+
+def _contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+class FP8GroupedGemmBlockFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+        assert config.granularity == ScalingGranularity.BLOCKWISE
+        assert config.block_size in [128], "Only block_size 128 is supported currently."
+        assert a.ndim == 2, "Input tensor must be 2-dimensional."
+        assert b.ndim == 3, "Weight tensor must be 3-dimensional."
+        assert group_lens.size(0) == b.size(0), "group_lens size must match b size(0)."
+        assert out_dtype in [torch.float16, torch.bfloat16]
+        dt = _get_fp8_dtype(config.format, True)
+        # one read of a -> 1x128 row copy (forward) + segment-padded 128x1 column copy (wgrad)
+        a_row, a_col, a_s_row, a_s_col, _, _ = quant_fp8_blockwise_segment_m_row_col_impl(
+            _contig(a), dt, config.block_size, group_lens, group_offs
+        )
+        b8, b_s = quant_fp8_blockwise_for_weight_impl(b, dt, block_size=config.block_size)
+        out = grouped_gemm_fp8_impl(
+            a_row, b8, a_s_row, b_s, group_lens, group_offs, trans_a=False, trans_b=trans_b, out_dtype=out_dtype,
+            granularity=config.granularity.value, num_cu=num_cu,
+        )
+        ctx.save_for_backward(a_col, a_s_col, b8, b_s, group_lens, group_offs)
+        ctx.trans_b, ctx.config, ctx.out_dtype, ctx.num_cu = trans_b, config, out_dtype, num_cu
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        grad_out = _contig(grad_out)
+        a_col, a_s_col, b8, b_s, group_lens, group_offs = ctx.saved_tensors
+        cfg = ctx.config
+        g_row, g_col, g_s_row, g_s_col, vk_lens, vk_offs = quant_fp8_blockwise_segment_m_row_col_impl(
+            grad_out, _get_fp8_dtype(cfg.format, False), cfg.block_size, group_lens, group_offs
+        )
+        grad_a = grouped_gemm_fp8_impl(
+            g_row, b8, g_s_row, b_s, group_lens, group_offs, trans_a=False, trans_b=not ctx.trans_b,
+            out_dtype=ctx.out_dtype, granularity=cfg.granularity.value, num_cu=ctx.num_cu,
+        )
+        grad_b = grouped_gemm_fp8_variable_k_impl(
+            a_col, g_col, a_s_col, g_s_col, vk_lens, vk_offs, trans_a=True, trans_b=False, trans_c=ctx.trans_b,
+            out_dtype=ctx.out_dtype, granularity=cfg.granularity.value, num_cu=ctx.num_cu,
+        )
+        return grad_a, grad_b, None, None, None, None, None, None
+
+
+class FP8GroupedGemmRowFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, a_t, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+        assert config.granularity == ScalingGranularity.ROWWISE
+        g = config.granularity
+        dt = _get_fp8_dtype(config.format, True)
+        if isinstance(a, QuantizedTensor):
+            assert a._is_grouped_tensor, "A QuantizedTensor input must be a grouped tensor"
+            check_quantized_tensor(a, config, axis=-1)
+            qa, group_offs = a, a.group_offs
+        else:
+            qa = QuantizedTensor.quantize(a, dt, g, axis=-1, block_size=config.block_size, group_lens=group_lens)
+        b_row_axis, b_col_axis = (-1, -2) if trans_b else (-2, -1)
+        if isinstance(b, QuantizedTensor):
+            assert not b._is_grouped_tensor, "B QuantizedTensor input must not be a grouped tensor"
+            check_quantized_tensor(b, config, axis=b_row_axis)
+            qb = b
+        else:
+            qb = QuantizedTensor.quantize(b, dt, g, axis=b_row_axis, block_size=config.block_size)
+        out = grouped_gemm_fp8_impl(
+            qa.qdata, qb.qdata, qa.scale_inv, qb.scale_inv, group_lens, group_offs, trans_a=False, trans_b=trans_b,
+            out_dtype=out_dtype, granularity=g.value, num_cu=num_cu,
+        )
+        # backward companions: re-quantise the dequantised forward operands along the other axis
+        qa_t = a_t if a_t is not None else QuantizedTensor.quantize(
+            qa.dequantize(), qa.real_dtype, g, axis=-2, block_size=config.block_size, group_lens=group_lens
+        )
+        qb_t = b_t if b_t is not None else QuantizedTensor.quantize(
+            qb.dequantize(), qb.real_dtype, g, axis=b_col_axis, block_size=config.block_size
+        )
+        ctx.save_for_backward(qa_t.qdata, qb_t.qdata, qa_t.scale_inv, qb_t.scale_inv, group_lens, group_offs)
+        ctx.trans_b, ctx.config, ctx.out_dtype, ctx.num_cu = trans_b, config, out_dtype, num_cu
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        grad_out = _contig(grad_out)
+        a_col, b_col, a_s_col, b_s_col, group_lens, group_offs = ctx.saved_tensors
+        cfg = ctx.config
+        g = cfg.granularity
+        gdt = _get_fp8_dtype(cfg.format, False)
+        qg = QuantizedTensor.quantize(grad_out, gdt, g, axis=-1, block_size=cfg.block_size, group_lens=group_lens)
+        grad_a = grouped_gemm_fp8_impl(
+            qg.qdata, b_col, qg.scale_inv, b_s_col, group_lens, group_offs, trans_a=False, trans_b=not ctx.trans_b,
+            out_dtype=ctx.out_dtype, granularity=g.value, num_cu=ctx.num_cu,
+        )
+        qg_t = QuantizedTensor.quantize(grad_out, gdt, g, axis=-2, block_size=cfg.block_size, group_lens=group_lens)
+        grad_b = grouped_gemm_fp8_variable_k_impl(
+            a_col, qg_t.qdata, a_s_col, qg_t.scale_inv, group_lens, group_offs, trans_a=True, trans_b=False,
+            trans_c=ctx.trans_b, out_dtype=ctx.out_dtype, granularity=g.value, num_cu=ctx.num_cu,
+        )
+        return grad_a, grad_b, None, None, None, None, None, None, None, None
+
+
+class FP8GroupedGemmTensorFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, a_t, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+        assert config.granularity == ScalingGranularity.TENSORWISE
+        g = config.granularity
+        dt = _get_fp8_dtype(config.format, True)
+        if isinstance(a, QuantizedTensor):
+            assert a._is_grouped_tensor, "A QuantizedTensor input must be a grouped tensor"
+            check_quantized_tensor(a, config)
+            qa, group_offs = a, a.group_offs
+        else:
+            qa = QuantizedTensor.quantize(a, dt, g, axis=-1, block_size=config.block_size, group_lens=group_lens)
+        if isinstance(b, QuantizedTensor):
+            assert not b._is_grouped_tensor, "B QuantizedTensor input must not be a grouped tensor"
+            check_quantized_tensor(b, config)
+            qb = b
+        else:
+            qb = QuantizedTensor.quantize(b, dt, g, axis=-1, block_size=config.block_size)
+        out = grouped_gemm_fp8_impl(
+            qa.qdata, qb.qdata, qa.scale_inv, qb.scale_inv, group_lens, group_offs, trans_a=False, trans_b=trans_b,
+            out_dtype=out_dtype, granularity=g.value, num_cu=num_cu,
+        )
+        # the tensor cores read b transposed in place, so backward reuses the forward payload
+        ctx.save_for_backward(qa.qdata, qb.qdata, qa.scale_inv, qb.scale_inv, group_lens, group_offs)
+        ctx.trans_b, ctx.config, ctx.out_dtype, ctx.num_cu = trans_b, config, out_dtype, num_cu
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        grad_out = _contig(grad_out)
+        a8, b8, a_s, b_s, group_lens, group_offs = ctx.saved_tensors
+        cfg = ctx.config
+        g = cfg.granularity
+        qg = QuantizedTensor.quantize(
+            grad_out, _get_fp8_dtype(cfg.format, False), g, axis=-1, block_size=cfg.block_size, group_lens=group_lens
+        )
+        grad_a = grouped_gemm_fp8_impl(
+            qg.qdata, b8, qg.scale_inv, b_s, group_lens, group_offs, trans_a=False, trans_b=not ctx.trans_b,
+            out_dtype=ctx.out_dtype, granularity=g.value, num_cu=ctx.num_cu,
+        )
+        grad_b = grouped_gemm_fp8_variable_k_impl(
+            a8, qg.qdata, a_s, qg.scale_inv, group_lens, group_offs, trans_a=True, trans_b=False,
+            trans_c=ctx.trans_b, out_dtype=ctx.out_dtype, granularity=g.value, num_cu=ctx.num_cu,
+        )
+        return grad_a, grad_b, None, None, None, None, None, None, None, None
+
+
+@torch._dynamo.disable(recursive=True, reason="builds QuantizedTensor wrappers inside autograd.Function.forward")
+def grouped_gemm_fp8(
+    a: Union[torch.Tensor, QuantizedTensor, QuantizedTensorPair],
+    b: Union[torch.Tensor, QuantizedTensor, QuantizedTensorPair],
+    group_lens: torch.Tensor,
+    group_offs: Optional[torch.Tensor] = None,
+    trans_b: bool = True,
+    out_dtype: Optional[torch.dtype] = None,
+    config: Optional[Float8QuantConfig] = None,
+    num_cu: Optional[int] = None,
+) -> torch.Tensor:
+    """Grouped GEMM ``out[rows of group g] = a[rows of group g] @ op(b[g])`` in FP8.
+
+    group_lens: CUDA int64 ``[G]``; group_offs (optional): its exclusive prefix sum ``[G+1]``.
+    ``num_cu`` caps the number of SMs the persistent kernel occupies.  Rows of the output at or
+    beyond ``sum(group_lens)`` are zero.
+    """
+    if config is None:
+        config = Float8QuantConfig()
+    if group_offs is None:
+        group_offs = group_offs_from_lens(group_lens)
+    a_data, a_data_t = (a.data, a.data_t) if isinstance(a, QuantizedTensorPair) else (a, None)
+    b_data, b_data_t = (b.data, b.data_t) if isinstance(b, QuantizedTensorPair) else (b, None)
+    if out_dtype is None:
+        out_dtype = torch.promote_types(a_data.dtype, b_data.dtype)
+    if config.granularity == ScalingGranularity.TENSORWISE:
+        return FP8GroupedGemmTensorFunc.apply(
+            a_data, b_data, a_data_t, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu
+        )
+    if config.granularity == ScalingGranularity.ROWWISE:
+        return FP8GroupedGemmRowFunc.apply(
+            a_data, b_data, a_data_t, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu
+        )
+    if config.granularity == ScalingGranularity.BLOCKWISE:
+        return FP8GroupedGemmBlockFunc.apply(a, b, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
+    raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

@@ -1,0 +1,93 @@
+"""Public FP8 quantize / dequantize ops (signatures of primus_turbo/pytorch/ops/quantization.py:52-269)."""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
+from primus_turbo_b200.pytorch.kernels.quantization_impl import (
+    dequant_fp8_blockwise_for_weight_impl,
+    dequant_fp8_blockwise_impl,
+    dequantize_fp8_rowwise_impl,
+    dequantize_fp8_tensorwise_impl,
+    quant_fp8_blockwise_dual_impl,
+    quant_fp8_blockwise_for_weight_impl,
+    quant_fp8_blockwise_impl,
+    quantize_fp8_rowwise_impl,
+    quantize_fp8_tensorwise_impl,
+)
+
+__all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8"]
+
+
+def quantize_fp8(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    *,
+    block_size: Optional[int] = None,
+    axis: Optional[int] = None,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(x_fp8, scale_inv)``.
+
+    TENSORWISE: one scale.  ROWWISE: ``axis`` required, scale_inv keeps x's shape with 1 on axis.
+    BLOCKWISE: ``block_size`` (128) required; ``scaling_recipe.use_2d_block`` selects one scale per
+    128x128 tile (weights), otherwise ``axis`` picks 1x128 (axis 1/-1) or 128x1 (axis 0/-2) blocks.
+    """
+    if granularity == ScalingGranularity.TENSORWISE:
+        return quantize_fp8_tensorwise_impl(x, out_dtype)
+    if granularity == ScalingGranularity.ROWWISE:
+        if axis is None:
+            raise ValueError("axis must be specified for rowwise FP8 quantization")
+        return quantize_fp8_rowwise_impl(x, out_dtype, axis)
+    if granularity == ScalingGranularity.BLOCKWISE:
+        assert block_size is not None, "block_size must be specified for BLOCKWISE quantization"
+        if scaling_recipe is not None and scaling_recipe.use_2d_block:
+            return quant_fp8_blockwise_for_weight_impl(x, out_dtype, block_size=block_size)
+        assert axis is not None, "axis must be specified for 1D BLOCKWISE quantization"
+        return quant_fp8_blockwise_impl(x, out_dtype, axis=axis, block_size=block_size)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def quantize_fp8_with_trans(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    *,
+    block_size: Optional[int] = None,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+    scaling_recipe_for_trans: Optional[ScalingRecipe] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """One read of x -> (row copy, row scales [M, N/128], column copy [M,N], column scales [M/128, N])."""
+    if granularity == ScalingGranularity.BLOCKWISE:
+        assert block_size is not None, "block_size must be specified for BLOCKWISE quantization"
+        return quant_fp8_blockwise_dual_impl(x, out_dtype, block_size=block_size)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def dequantize_fp8(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    *,
+    block_size: Optional[int] = None,
+    axis: Optional[int] = None,
+    scale_inv: torch.Tensor,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+) -> torch.Tensor:
+    if granularity == ScalingGranularity.TENSORWISE:
+        return dequantize_fp8_tensorwise_impl(x, out_dtype, scale_inv)
+    if granularity == ScalingGranularity.ROWWISE:
+        if axis is None:
+            raise ValueError("axis must be specified for rowwise FP8 de-quantization")
+        return dequantize_fp8_rowwise_impl(x, out_dtype, axis, scale_inv)
+    if granularity == ScalingGranularity.BLOCKWISE:
+        assert block_size is not None, "block_size must be specified for BLOCKWISE de-quantization"
+        if scaling_recipe is not None and scaling_recipe.use_2d_block:
+            return dequant_fp8_blockwise_for_weight_impl(x, scale_inv, out_dtype, block_size)
+        assert axis is not None, "axis must be specified for 1D BLOCKWISE de-quantization"
+        return dequant_fp8_blockwise_impl(x, scale_inv, out_dtype, axis, block_size)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
