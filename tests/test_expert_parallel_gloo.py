@@ -1,0 +1,93 @@
+"""CPU, world_size 2 over gloo: the expert-parallel exchange (count all-gather, row all-to-all,
+expert-major permutation and the way back) against a single-process evaluation, forward and
+backward, including experts that receive no rows."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+WORLD = 2
+E = 6  # 3 experts per rank
+H = 5
+
+
+def _routing(seed):
+    g = torch.Generator().manual_seed(seed)
+    counts = torch.randint(0, 7, (WORLD, E), generator=g)
+    counts[:, 1] = 0  # an expert nobody routes to
+    counts[1, 4] = 0
+    xs = [torch.randn(int(counts[r].sum()), H, generator=g, dtype=torch.float64) for r in range(WORLD)]
+    return counts, xs
+
+
+def _expert_fn(e_global: int, rows: torch.Tensor) -> torch.Tensor:
+    return rows * (e_global + 1.0) + rows.pow(2) * 0.5
+
+
+def _worker(rank, store_path, seed, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    store = dist.FileStore(store_path, WORLD)
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=WORLD)
+    try:
+        from primus_turbo_b200.pytorch.dist.expert_parallel import build_exchange_plan, expert_parallel_apply
+
+        counts, xs = _routing(seed)
+        x = xs[rank].clone().requires_grad_(True)
+        e_loc = E // WORLD
+
+        def local_fn(rows, group_lens):
+            assert group_lens.tolist() == counts[:, rank * e_loc : (rank + 1) * e_loc].sum(0).tolist()
+            outs, start = [], 0
+            for i, n in enumerate(group_lens.tolist()):
+                outs.append(_expert_fn(rank * e_loc + i, rows[start : start + n]))
+                start += n
+            return torch.cat(outs) if outs else rows
+
+        plan = build_exchange_plan(counts[rank])
+        assert plan.send_splits == counts[rank].view(WORLD, e_loc).sum(1).tolist()
+        y = expert_parallel_apply(x, counts[rank], local_fn, plan=plan)
+        coeff = torch.arange(y.numel(), dtype=torch.float64).view_as(y) * 1e-2 + 1.0
+        (y * coeff).sum().backward()
+        out_q.put((rank, y.detach().tolist(), x.grad.tolist()))  # plain lists: no shared-memory handles
+        dist.barrier()
+    except Exception as exc:  # surface the failure instead of letting the parent wait for a result
+        out_q.put((rank, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_expert_parallel_exchange_world2(seed):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_worker, args=(r, path, seed, q)) for r in range(WORLD)]
+        for p in procs:
+            p.start()
+        results = {}
+        for _ in range(WORLD):
+            r, y, gx = q.get(timeout=120)
+            assert gx is not None, f"rank {r} failed: {y}"
+            results[r] = (torch.tensor(y, dtype=torch.float64).reshape(-1, H), torch.tensor(gx, dtype=torch.float64).reshape(-1, H))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    counts, xs = _routing(seed)
+    for r in range(WORLD):
+        x = xs[r].clone().requires_grad_(True)
+        outs, start = [], 0
+        for e in range(E):
+            n = int(counts[r, e])
+            outs.append(_expert_fn(e, x[start : start + n]))
+            start += n
+        y_ref = torch.cat(outs)
+        coeff = torch.arange(y_ref.numel(), dtype=torch.float64).view_as(y_ref) * 1e-2 + 1.0
+        (y_ref * coeff).sum().backward()
+        assert torch.equal(results[r][0], y_ref.detach())
+        assert torch.allclose(results[r][1], x.grad, rtol=0, atol=0)
