@@ -86,7 +86,8 @@ def check(rc: int, what: str) -> None:
 
 
 # kernels enqueued by one successful call of each entry point (memset nodes not counted)
-KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_gemm_status": 0}
+KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_segment_row_col": 2,
+                    "ptb_gemm_status": 0}
 launch_count = 0  # running total of kernels this process enqueued through the C ABI
 _event_log = None  # when a dict: name -> [(start_event, stop_event), ...] on the launching stream
 

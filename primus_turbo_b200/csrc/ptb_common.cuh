@@ -74,11 +74,9 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 }
 
 // q = cast_rne(clamp(x * scale, -fmax, fmax)).  The multiply is a single fp32 operation (nothing
-// to contract it with) and the clamp uses fminf/fmaxf exactly as the value path requires.
-template <int FMT> __device__ __forceinline__ float quant_val(float x, float scale) {
-    float v = x * scale;
-    return fmaxf(fminf(v, Fp8Max<FMT>::v), -Fp8Max<FMT>::v);
-}
+// to contract it with).  The clamp itself is performed by the conversion: cvt.rn.satfinite maps
+// every finite value beyond +-fmax to +-fmax, which is exactly what clamping first would give.
+template <int FMT> __device__ __forceinline__ float quant_val(float x, float scale) { return x * scale; }
 
 // two fp32 -> two fp8 bytes (low byte = first value), round-to-nearest-even, finite saturation
 template <int FMT> __device__ __forceinline__ uint16_t cvt_fp8x2(float lo, float hi) {

@@ -16,18 +16,34 @@
 // kernel records a status word, drains its own copies and leaves normally.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "ptb_common.cuh"
 
 namespace ptb {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int kStages     = 4;
+constexpr int BM = 128, BK = 128;
 constexpr int kThreads    = 384;
 constexpr int kABytes     = BM * BK;              // 16 KiB
-constexpr int kBBytes     = BN * BK;              // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;    // 48 KiB
-constexpr int kMaxGroups  = 2048;                 // tile table entries kept in shared memory
+constexpr int kMaxStages  = 8;
+constexpr int kMaxAccBufs = 4;
+
+// Compile-time geometry of one tile width.  BN = 256: two 256-column TMEM buffers, 3 stages of 48 KiB.
+// BN = 128: four 128-column TMEM buffers (the promotion warps get three K-blocks of slack before the
+// tensor core needs a buffer back) and 5 stages of 32 KiB.
+// DEEP = 1 trades the output staging buffer for one more pipeline stage (plain stores in the epilogue).
+template <int BN, int DEEP> struct Geo {
+    static constexpr int kBBytes      = BN * BK;
+    static constexpr int kStageBytes  = kABytes + kBBytes;
+    static constexpr int kStages      = (BN == 256 ? 3 : 5) + DEEP;
+    static constexpr int kAccBufs     = 512 / BN;
+    static constexpr int kWgCols      = BN / 2;             // columns owned by one epilogue warpgroup
+    static constexpr int kChunks      = kWgCols / 32;       // 32-column TMEM loads per partial
+    static constexpr int kWarpCBytes  = 32 * kWgCols * 2;   // staging of one warp's 32-row slab (16-bit out)
+    static constexpr int kCStageBytes = DEEP ? 0 : 8 * kWarpCBytes;
+};
+constexpr int kMaxGroups  = 1024;                 // tile table entries kept in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
 
 constexpr int kScaleTensor = 0, kScaleRow = 1, kScaleBlock2D = 2, kScaleBlock1D = 3;
@@ -39,10 +55,15 @@ __device__ int g_gemm_status = 0;
 struct GemmArgs {
     CUtensorMap tm_a;
     CUtensorMap tm_b;
+    CUtensorMap tm_c; // output, 16-bit elements, {64 columns, 32 rows} boxes (only when use_tma_store)
+    int use_tma_store;
+    int debug; // PTB_GEMM_DEBUG bits (timing experiments only): 1 skip promotion FMAs, 2 skip TMEM loads, 4 skip stores
     int kind;
     int a_mn, b_mn; // 1: operand stored with the contraction axis strided (MN-major)
     uint32_t idesc;
     int M, N, K, G;
+    int bn; // tile width the kernel was instantiated with
+    int deep; // 1: four-stage variant without output staging
     int tiles_n;
     const int64_t *group_offs;
     void *c;
@@ -98,6 +119,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tm,
                  "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tm), "r"(src),
+                 "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -155,11 +185,12 @@ struct Tile {
 struct Schedule {
     const GemmArgs &a;
     const int *tile_prefix; // shared: cumulative m-tiles per group (grouped rows) [G+1]
+    const int *offs;        // shared: group offsets [G+1]
     int total;
     int cursor_g;
 
-    __device__ Schedule(const GemmArgs &args, const int *prefix, int total_tiles)
-        : a(args), tile_prefix(prefix), total(total_tiles), cursor_g(0) {}
+    __device__ Schedule(const GemmArgs &args, const int *prefix, const int *group_offs, int total_tiles)
+        : a(args), tile_prefix(prefix), offs(group_offs), total(total_tiles), cursor_g(0) {}
 
     __device__ bool get(int t, Tile &o) {
         if (t >= total) return false;
@@ -173,25 +204,24 @@ struct Schedule {
             const int rows    = min(8, tiles_m - first);
             const int r       = t - gi * band;
             const int mt = first + r % rows, nt = r / rows;
-            o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * BN; o.g = 0; o.k_row0 = 0;
+            o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * a.bn; o.g = 0; o.k_row0 = 0;
             o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
         } else if (a.kind == kKindGroupedRows) {
             const int mbi = t / a.tiles_n, nt = t - mbi * a.tiles_n;
             while (tile_prefix[cursor_g + 1] <= mbi) ++cursor_g;
-            const int g        = cursor_g;
-            const int64_t lo   = a.group_offs[g];
-            const int64_t hi   = a.group_offs[g + 1];
-            o.m0 = (int) lo + (mbi - tile_prefix[g]) * BM; o.m_end = (int) hi; o.n0 = nt * BN; o.g = g;
+            const int g  = cursor_g;
+            const int lo = offs[g], hi = offs[g + 1];
+            o.m0 = lo + (mbi - tile_prefix[g]) * BM; o.m_end = hi; o.n0 = nt * a.bn; o.g = g;
             o.k_row0 = 0; o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
         } else {
             const int tiles_m = (a.M + BM - 1) / BM;
             const int per_g   = tiles_m * a.tiles_n;
             const int g = t / per_g, r = t - g * per_g;
             const int mt = r / a.tiles_n, nt = r - mt * a.tiles_n;
-            const int64_t lo = a.group_offs[g], hi = a.group_offs[g + 1];
-            o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * BN; o.g = g; o.k_row0 = (int) lo;
-            o.num_kb = (int) ((hi - lo + BK - 1) / BK);
-            o.k_tail = (int) ((hi - lo) % BK);
+            const int lo = offs[g], hi = offs[g + 1];
+            o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * a.bn; o.g = g; o.k_row0 = lo;
+            o.num_kb = (hi - lo + BK - 1) / BK;
+            o.k_tail = (hi - lo) % BK;
         }
         return true;
     }
@@ -227,23 +257,29 @@ template <> struct Pack8<float> {
     }
 };
 
-struct __align__(8) SharedCtl {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
+struct __align__(16) SharedCtl {
+    float col_scale[8][2][128]; // [epilogue warp][parity][column]: private to a warp, no cross-warp barrier
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[kMaxAccBufs];
+    uint64_t tmem_empty[kMaxAccBufs];
     uint32_t tmem_base;
     int total_tiles;
-    float col_scale[8][2][128]; // [epilogue warp][parity][column]: private to a warp, no cross-warp barrier
     int tile_prefix[kMaxGroups + 1];
+    int group_offs[kMaxGroups + 1]; // copy of the device offsets: the schedule never waits on global memory
 };
 
-template <int SCALE, typename OutT>
+template <int SCALE, typename OutT, int BN, int DEEP>
 __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
+    using G_ = Geo<BN, DEEP>;
+    constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes, kBBytes = G_::kBBytes;
+    constexpr int kAccBufs = G_::kAccBufs, kWgCols = G_::kWgCols, kChunks = G_::kChunks;
+    constexpr int kCStageBytes = G_::kCStageBytes;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t *smem  = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    SharedCtl *ctl = reinterpret_cast<SharedCtl *>(smem + kStages * kStageBytes);
+    uint8_t *c_stage = smem + kStages * kStageBytes;
+    SharedCtl *ctl   = reinterpret_cast<SharedCtl *>(c_stage + kCStageBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = smem_u32(smem);
@@ -255,12 +291,15 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kAccBufs; ++b) {
             mbar_init(smem_u32(&ctl->tmem_full[b]), 1);
             mbar_init(smem_u32(&ctl->tmem_empty[b]), 8); // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (args.kind != kKindDense) {
+        for (int g = threadIdx.x; g <= args.G; g += kThreads) ctl->group_offs[g] = (int) args.group_offs[g];
     }
     if (args.kind == kKindGroupedRows) {
         // cumulative 128-row tiles per group; one warp scans (G <= kMaxGroups, checked on the host)
@@ -301,10 +340,10 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
     const int total_tiles    = ctl->total_tiles;
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
-            Schedule sched(args, ctl->tile_prefix, total_tiles);
+            Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
             Tile t;
             uint32_t it = 0; // ring position over the whole kernel
             bool ok     = true;
@@ -322,7 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                     else           tma_load_3d(sa, &args.tm_a, full, k, t.m0, 0);
                     if (args.b_mn) {
                         tma_load_3d(sb, &args.tm_b, full, t.n0, k, gb);
-                        tma_load_3d(sb + kBBytes / 2, &args.tm_b, full, t.n0 + 128, k, gb);
+                        if constexpr (BN == 256) tma_load_3d(sb + 16384, &args.tm_b, full, t.n0 + 128, k, gb);
                     } else {
                         tma_load_3d(sb, &args.tm_b, full, k, t.n0, gb);
                     }
@@ -339,21 +378,21 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             }
         } else if (warp == 1) {
             // ================= MMA issuer (whole warp walks the schedule, lane 0 issues) =================
-            Schedule sched(args, ctl->tile_prefix, total_tiles);
+            Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
             Tile t;
             uint32_t it = 0, acc_it = 0;
             bool ok     = true;
             const uint32_t a_lbo = 0, a_sbo = 1024, a_step = args.a_mn ? 4096u : 32u;
-            const uint32_t b_lbo = args.b_mn ? (uint32_t) (kBBytes / 2) : 0u, b_sbo = 1024;
+            const uint32_t b_lbo = args.b_mn ? 16384u : 0u, b_sbo = 1024;
             const uint32_t b_step = args.b_mn ? 4096u : 32u;
             for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
                 for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     const bool new_acc = kPerBlock || kb == 0;
-                    const uint32_t buf = acc_it & 1;
+                    const uint32_t buf = acc_it % kAccBufs;
                     if (new_acc) {
-                        if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), ((acc_it >> 1) & 1) ^ 1)) { ok = false; break; }
+                        if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), ((acc_it / kAccBufs) & 1) ^ 1)) { ok = false; break; }
                     }
                     if (!mbar_wait(smem_u32(&ctl->full[s]), ph)) { ok = false; break; }
                     uint8_t *a_tile = smem + s * kStageBytes;
@@ -389,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ================= promotion + epilogue warpgroups =================
         const int wg   = (warp - 4) >> 2;         // column half
         const int quad = warp & 3;                // TMEM lane quadrant this warp may read
@@ -407,95 +446,200 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             }
         }
 
-        Schedule sched(args, ctl->tile_prefix, total_tiles);
+        Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
         Tile t;
         uint32_t acc_it = 0;
         bool ok         = true;
         const bool vec_store = ((args.ldc * sizeof(OutT)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(args.c) & 15u) == 0) &&
                                ((args.c_group_stride * sizeof(OutT)) % 16 == 0);
-        float acc[128];
+        const bool tma_store  = (sizeof(OutT) == 2) && args.use_tma_store && !DEEP;
+        uint8_t *my_stage     = c_stage + (warp - 4) * G_::kWarpCBytes;
+        bool store_pending    = false;
+        float acc[kWgCols];
         for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
             const int gb      = (args.kind == kKindGroupedRows) ? t.g : 0;
             const int row     = t.m0 + row_in_tile;
-            const int col0    = t.n0 + wg * 128;
+            const int col0    = t.n0 + wg * kWgCols;
             const int segs    = kPerBlock ? t.num_kb : (t.num_kb > 0 ? 1 : 0);
             const int kb_base = t.k_row0 / BK;
 #pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < kWgCols; ++j) acc[j] = 0.0f;
 
-            for (int sidx = 0; sidx < segs; ++sidx, ++acc_it) {
-                const uint32_t buf = acc_it & 1;
-                float s_row = 1.0f;
+            // Scales are fetched two contraction blocks ahead of their use so that the global-load
+            // latency never sits between a finished partial product and its promotion.
+            const float *a_sp = args.a_scale + (int64_t) min(row, t.m_end - 1) * args.as_m + (int64_t) kb_base * args.as_k;
+            const float *b_sp = args.b_scale;
+            if constexpr (SCALE == kScaleBlock2D)
+                b_sp += (int64_t) gb * args.bs_g + (int64_t) (col0 / 128) * args.bs_n;
+            if constexpr (SCALE == kScaleBlock1D) b_sp += (int64_t) kb_base * args.bs_k;
+            float sa0 = 0.f, sa1 = 0.f, sb0 = 0.f, sb1 = 0.f;
+            float csn[4] = {0.f, 0.f, 0.f, 0.f};
+            float *cs_buf = &ctl->col_scale[warp - 4][0][0];
+            if constexpr (kPerBlock) {
+                if (segs > 0) sa0 = a_sp[0];
+                if (segs > 1) sa1 = a_sp[args.as_k];
                 if constexpr (SCALE == kScaleBlock2D) {
-                    const float sa = args.a_scale[(int64_t) min(row, t.m_end - 1) * args.as_m + (int64_t) sidx * args.as_k];
-                    const float sb = args.b_scale[(int64_t) gb * args.bs_g + (int64_t) (col0 / 128) * args.bs_n +
-                                                  (int64_t) sidx * args.bs_k];
-                    s_row = sa * sb;
-                } else if constexpr (SCALE == kScaleBlock1D) {
-                    const int64_t kbg = kb_base + sidx;
-                    s_row = args.a_scale[(int64_t) min(row, t.m_end - 1) * args.as_m + kbg * args.as_k];
-                    float *cs = ctl->col_scale[warp - 4][sidx & 1];
+                    if (segs > 0) sb0 = b_sp[0];
+                    if (segs > 1) sb1 = b_sp[args.bs_k];
+                } else if (segs > 0) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < kChunks; ++q) {
                         const int c = col0 + q * 32 + lane;
-                        cs[q * 32 + lane] = (c < args.N) ? args.b_scale[(int64_t) c * args.bs_n + kbg * args.bs_k] : 0.0f;
+                        cs_buf[q * 32 + lane] = (c < args.N) ? b_sp[(int64_t) c * args.bs_n] : 0.0f;
                     }
                     __syncwarp();
                 }
-                if (!mbar_wait(smem_u32(&ctl->tmem_full[buf]), (acc_it >> 1) & 1)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t) (quad * 32) << 16) + buf * BN + wg * 128;
+            }
+
+            for (int sidx = 0; sidx < segs; ++sidx, ++acc_it) {
+                const uint32_t buf = acc_it % kAccBufs;
+                float s_row        = 1.0f;
+                if constexpr (kPerBlock) {
+                    s_row = (SCALE == kScaleBlock2D) ? sa0 * sb0 : sa0;
+                    sa0   = sa1;
+                    sb0   = sb1;
+                    if (sidx + 2 < segs) {
+                        sa1 = a_sp[(int64_t) (sidx + 2) * args.as_k];
+                        if constexpr (SCALE == kScaleBlock2D) sb1 = b_sp[(int64_t) (sidx + 2) * args.bs_k];
+                    }
+                    if constexpr (SCALE == kScaleBlock1D) {
+                        if (sidx + 1 < segs) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float v[32];
-                    tc_ld32(taddr + c * 32, v);
-                    tc_wait_ld();
-                    if constexpr (SCALE == kScaleBlock2D) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(v[j], s_row, acc[c * 32 + j]);
-                    } else if constexpr (SCALE == kScaleBlock1D) {
-                        const float *cs = &ctl->col_scale[warp - 4][sidx & 1][c * 32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(v[j] * s_row, cs[j], acc[c * 32 + j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = v[j];
+                            for (int q = 0; q < kChunks; ++q) {
+                                const int c = col0 + q * 32 + lane;
+                                csn[q]      = (c < args.N) ? b_sp[(int64_t) c * args.bs_n + (int64_t) (sidx + 1) * args.bs_k] : 0.0f;
+                            }
+                        }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
+                if (!mbar_wait(smem_u32(&ctl->tmem_full[buf]), (acc_it / kAccBufs) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t) (quad * 32) << 16) + buf * BN + wg * kWgCols;
+                const float *cs      = cs_buf + (sidx & 1) * 128;
+                const float2 s_row2  = make_float2(s_row, s_row);
+                // two 32-column loads in flight; the second pair is issued while the first is consumed
+                float v0[32], v1[32];
+                if (args.debug & 2) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
+                    continue;
+                }
+                tc_ld32(taddr, v0);
+                tc_ld32(taddr + 32, v1);
+                tc_wait_ld();
+// packed fp32x2 arithmetic: half the issue slots of scalar FMA for the same IEEE results
+#define PTB_PROMOTE(V, C)                                                                                      \
+    if (!(args.debug & 1)) _Pragma("unroll") for (int j = 0; j < 8; ++j) {                                      \
+        float2 a0 = make_float2(acc[(C) * 32 + 4 * j], acc[(C) * 32 + 4 * j + 1]);                              \
+        float2 a1 = make_float2(acc[(C) * 32 + 4 * j + 2], acc[(C) * 32 + 4 * j + 3]);                          \
+        const float2 x0 = make_float2(V[4 * j], V[4 * j + 1]), x1 = make_float2(V[4 * j + 2], V[4 * j + 3]);     \
+        if constexpr (SCALE == kScaleBlock2D) {                                                                 \
+            a0 = __ffma2_rn(x0, s_row2, a0);                                                                    \
+            a1 = __ffma2_rn(x1, s_row2, a1);                                                                    \
+        } else if constexpr (SCALE == kScaleBlock1D) {                                                          \
+            const float4 c4 = *reinterpret_cast<const float4 *>(cs + (C) * 32 + 4 * j);                          \
+            a0 = __ffma2_rn(__fmul2_rn(x0, s_row2), make_float2(c4.x, c4.y), a0);                               \
+            a1 = __ffma2_rn(__fmul2_rn(x1, s_row2), make_float2(c4.z, c4.w), a1);                               \
+        } else {                                                                                                \
+            a0 = x0;                                                                                            \
+            a1 = x1;                                                                                            \
+        }                                                                                                       \
+        acc[(C) * 32 + 4 * j] = a0.x; acc[(C) * 32 + 4 * j + 1] = a0.y;                                         \
+        acc[(C) * 32 + 4 * j + 2] = a1.x; acc[(C) * 32 + 4 * j + 3] = a1.y;                                     \
+    }
+                if constexpr (kChunks == 4) {
+                    PTB_PROMOTE(v0, 0)
+                    tc_ld32(taddr + 64, v0);
+                    PTB_PROMOTE(v1, 1)
+                    tc_ld32(taddr + 96, v1);
+                    tc_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf])); // buffer may be overwritten now
+                    PTB_PROMOTE(v0, 2)
+                    PTB_PROMOTE(v1, 3)
+                } else {
+                    // the whole partial is in registers: hand the buffer back before doing any arithmetic
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
+                    PTB_PROMOTE(v0, 0)
+                    PTB_PROMOTE(v1, 1)
+                }
+#undef PTB_PROMOTE
+                if constexpr (SCALE == kScaleBlock1D) {
+                    if (sidx + 1 < segs) {
+                        float *nb = cs_buf + ((sidx + 1) & 1) * 128;
+#pragma unroll
+                        for (int q = 0; q < kChunks; ++q) nb[q * 32 + lane] = csn[q];
+                    }
+                    __syncwarp();
+                }
             }
             if (!ok) break;
 
-            // ---- scale (tensorwise / rowwise) and store ------------------------------------------
-            if (row < t.m_end) {
-                float sa = 1.0f;
-                if constexpr (SCALE == kScaleTensor) sa = args.a_scale[0] * args.b_scale[0];
-                if constexpr (SCALE == kScaleRow) sa = args.a_scale[(int64_t) row * args.as_m];
+            // ---- scale (tensorwise / rowwise), convert and store ---------------------------------
+            float sa = 1.0f;
+            if constexpr (SCALE == kScaleTensor) sa = args.a_scale[0] * args.b_scale[0];
+            if constexpr (SCALE == kScaleRow) sa = args.a_scale[(int64_t) min(row, t.m_end - 1) * args.as_m];
+            if constexpr (SCALE == kScaleTensor || SCALE == kScaleRow) {
+#pragma unroll
+                for (int j = 0; j < kWgCols; ++j) {
+                    float s = sa;
+                    if constexpr (SCALE == kScaleRow) {
+                        const int c = col0 + j;
+                        s = sa * ((c < args.N) ? args.b_scale[(int64_t) gb * args.bs_g + (int64_t) c * args.bs_n] : 0.0f);
+                    }
+                    acc[j] *= s;
+                }
+            }
+            const int warp_row0 = t.m0 + quad * 32;
+            if (args.debug & 4) continue;
+            if (tma_store && warp_row0 + 32 <= t.m_end) {
+                // whole 32-row slab is inside the tile's valid rows: stage it (128-byte swizzled) and
+                // let the copy engine write it; the tensor map clips columns past N
+                if constexpr (sizeof(OutT) == 2) {
+                    if (store_pending) {
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j8 = 0; j8 < kWgCols / 8; ++j8) {
+                        OutT *dst = reinterpret_cast<OutT *>(my_stage + (j8 >> 3) * 4096 + lane * 128 +
+                                                             (((j8 & 7) ^ (lane & 7)) << 4));
+                        Pack8<OutT>::store(dst, &acc[j8 * 8]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int gc = (args.kind == kKindGroupedK) ? t.g : 0;
+                        if (col0 < args.N) tma_store_3d(&args.tm_c, smem_u32(my_stage), col0, warp_row0, gc);
+                        if constexpr (kWgCols == 128) {
+                            if (col0 + 64 < args.N)
+                                tma_store_3d(&args.tm_c, smem_u32(my_stage + 4096), col0 + 64, warp_row0, gc);
+                        }
+                        tma_store_commit();
+                    }
+                    store_pending = true;
+                }
+            } else if (row < t.m_end) {
                 OutT *crow = cbase + (int64_t) t.g * args.c_group_stride + (int64_t) row * args.ldc;
 #pragma unroll
-                for (int j8 = 0; j8 < 16; ++j8) {
+                for (int j8 = 0; j8 < kWgCols / 8; ++j8) {
                     const int c = col0 + j8 * 8;
                     if (c >= args.N) continue;
-                    float o[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float s = sa;
-                        if constexpr (SCALE == kScaleRow)
-                            s = sa * ((c + j < args.N) ? args.b_scale[(int64_t) gb * args.bs_g + (int64_t) (c + j) * args.bs_n] : 0.0f);
-                        o[j] = (SCALE == kScaleTensor || SCALE == kScaleRow) ? acc[j8 * 8 + j] * s : acc[j8 * 8 + j];
-                    }
                     if (vec_store && c + 8 <= args.N) {
-                        Pack8<OutT>::store(crow + c, o);
+                        Pack8<OutT>::store(crow + c, &acc[j8 * 8]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (c + j < args.N) crow[c + j] = from_f32<OutT>(o[j]);
+                            if (c + j < args.N) crow[c + j] = from_f32<OutT>(acc[j8 * 8 + j]);
                     }
                 }
             }
         }
+        if (store_pending && lane == 0) tma_store_wait_all();
         if (!ok && lane == 0) atomicExch(&g_gemm_status, 3);
     }
 
@@ -548,7 +692,28 @@ int make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64
     return 0;
 }
 
-uint32_t make_idesc(int a_dtype, int b_dtype, int a_mn, int b_mn) {
+// Output map for the TMA-store epilogue: 16-bit elements, {64, 32, 1} boxes, 128-byte swizzle.
+// Returns 0 and sets *ok = 1 when the layout qualifies; otherwise the kernel stores directly.
+int make_c_map(CUtensorMap *tm, int *ok, void *c, int out_dtype, uint64_t cols, uint64_t rows, uint64_t groups,
+               uint64_t ldc, uint64_t group_stride) {
+    *ok = 0;
+    if (out_dtype != PTB_BF16 && out_dtype != PTB_F16) return 0;
+    if (!aligned16(c) || (ldc * 2) % 16 != 0 || (group_stride * 2) % 16 != 0) return 0;
+    EncodeTiledFn fn;
+    int rc = get_encode_fn(&fn);
+    if (rc) return rc;
+    cuuint64_t dims[3]    = {cols, rows ? rows : 1, groups ? groups : 1};
+    cuuint64_t strides[2] = {ldc * 2, (group_stride ? group_stride : ldc * (rows ? rows : 1)) * 2};
+    cuuint32_t box[3]     = {64, 32, 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    PTB_REQUIRE(r == CUDA_SUCCESS, PTB_ERR_DRIVER, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int) r);
+    *ok = 1;
+    return 0;
+}
+
+uint32_t make_idesc(int a_dtype, int b_dtype, int a_mn, int b_mn, int BN) {
     uint32_t d = 0;
     d |= 1u << 4;                                    // D format fp32
     d |= (a_dtype == PTB_E5M2 ? 1u : 0u) << 7;       // A format
@@ -560,11 +725,17 @@ uint32_t make_idesc(int a_dtype, int b_dtype, int a_mn, int b_mn) {
     return d;
 }
 
-constexpr size_t kSmemBytes = 1024 + (size_t) kStages * kStageBytes + sizeof(SharedCtl);
+template <int BN, int DEEP> constexpr size_t smem_bytes() {
+    return 1024 + (size_t) Geo<BN, DEEP>::kStages * Geo<BN, DEEP>::kStageBytes + Geo<BN, DEEP>::kCStageBytes +
+           sizeof(SharedCtl);
+}
+static_assert(smem_bytes<256, 0>() <= 232448 && smem_bytes<128, 0>() <= 232448 && smem_bytes<256, 1>() <= 232448,
+              "shared memory budget of one CTA exceeded");
 
-template <int SCALE, typename OutT> int launch_one(const GemmArgs &args, int grid, cudaStream_t st) {
+template <int SCALE, typename OutT, int BN, int DEEP> int launch_bn(const GemmArgs &args, int grid, cudaStream_t st) {
     static bool configured[64] = {}; // per device; the attribute set is idempotent, a race only repeats it
-    auto kfn = fp8_gemm_kernel<SCALE, OutT>;
+    constexpr size_t kSmemBytes = smem_bytes<BN, DEEP>();
+    auto kfn = fp8_gemm_kernel<SCALE, OutT, BN, DEEP>;
     int dev  = 0;
     PTB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -576,6 +747,11 @@ template <int SCALE, typename OutT> int launch_one(const GemmArgs &args, int gri
     return 0;
 }
 
+template <int SCALE, typename OutT> int launch_one(const GemmArgs &args, int grid, cudaStream_t st) {
+    if (args.bn == 128) return launch_bn<SCALE, OutT, 128, 0>(args, grid, st);
+    return args.deep ? launch_bn<SCALE, OutT, 256, 1>(args, grid, st) : launch_bn<SCALE, OutT, 256, 0>(args, grid, st);
+}
+
 template <int SCALE> int launch_scale(const GemmArgs &args, int out_dtype, int grid, cudaStream_t st) {
     switch (out_dtype) {
     case PTB_BF16: return launch_one<SCALE, __nv_bfloat16>(args, grid, st);
@@ -585,7 +761,11 @@ template <int SCALE> int launch_scale(const GemmArgs &args, int out_dtype, int g
     }
 }
 
-int launch_gemm(const GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cudaStream_t st) {
+int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cudaStream_t st) {
+    const char *dbg = getenv("PTB_GEMM_DEBUG");
+    args.debug      = dbg ? atoi(dbg) : 0;
+    const char *deep = getenv("PTB_GEMM_DEEP");
+    args.deep        = deep ? atoi(deep) : 0;
     int dev = 0, sms = 0;
     PTB_CUDA(cudaGetDevice(&dev));
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -597,6 +777,17 @@ int launch_gemm(const GemmArgs &args, int scale_mode, int out_dtype, int num_sms
     case kScaleBlock1D: return launch_scale<kScaleBlock1D>(args, out_dtype, grid, st);
     default: return fail(PTB_ERR_ARG, "unknown scale mode %d", scale_mode);
     }
+}
+
+// Tile width.  PTB_GEMM_BN=128|256 overrides (tuning experiments).
+int choose_bn(int scale_mode) {
+    const char *e = getenv("PTB_GEMM_BN");
+    if (e) {
+        const int v = atoi(e);
+        if (v == 128 || v == 256) return v;
+    }
+    (void) scale_mode;
+    return 256; // the 128-wide tile is shared-memory-bandwidth bound with one CTA per tile (measured)
 }
 
 int scale_mode_of(int granularity, int b_block_2d, int *mode) {
@@ -641,6 +832,8 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
     int rc = scale_mode_of(granularity, b_block_2d, &mode);
     if (rc) return rc;
     GemmArgs g{};
+    const int BN = choose_bn(mode);
+    g.bn         = BN;
     // A: [M,K] K-major, or [K,M] (trans_a) MN-major
     if (!trans_a) rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M, 1, (uint64_t) lda, (uint64_t) lda * M, BM);
     else          rc = make_map(&g.tm_a, a, (uint64_t) M, (uint64_t) K, 1, (uint64_t) lda, (uint64_t) lda * K, BK);
@@ -650,10 +843,12 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
     else         rc = make_map(&g.tm_b, b, (uint64_t) N, (uint64_t) K, 1, (uint64_t) ldb, (uint64_t) ldb * K, BK);
     if (rc) return rc;
     g.kind = kKindDense; g.a_mn = trans_a ? 1 : 0; g.b_mn = trans_b ? 0 : 1;
-    g.idesc = make_idesc(a_dtype, b_dtype, g.a_mn, g.b_mn);
+    g.idesc = make_idesc(a_dtype, b_dtype, g.a_mn, g.b_mn, BN);
     g.M = (int) M; g.N = (int) N; g.K = (int) K; g.G = 1;
     g.tiles_n = (int) cdiv<int64_t>(N, BN);
     g.c = c; g.ldc = ldc; g.c_group_stride = 0;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, c, c_dtype, (uint64_t) N, (uint64_t) M, 1, (uint64_t) ldc, 0);
+    if (rc) return rc;
     g.a_scale = a_scale; g.as_m = a_scale_stride_m; g.as_k = a_scale_stride_k;
     g.b_scale = b_scale; g.bs_g = 0; g.bs_n = b_scale_stride_n; g.bs_k = b_scale_stride_k;
     return launch_gemm(g, mode, c_dtype, num_sms, (cudaStream_t) stream);
@@ -676,17 +871,21 @@ int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b,
     int rc = scale_mode_of(granularity, 1, &mode);
     if (rc) return rc;
     GemmArgs g{};
+    const int BN = choose_bn(mode);
+    g.bn         = BN;
     rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M_total, 1, (uint64_t) lda, (uint64_t) lda * M_total, BM);
     if (rc) return rc;
     if (trans_b) rc = make_map(&g.tm_b, b, (uint64_t) K, (uint64_t) N, (uint64_t) G, (uint64_t) K, (uint64_t) K * N, BN);
     else         rc = make_map(&g.tm_b, b, (uint64_t) N, (uint64_t) K, (uint64_t) G, (uint64_t) N, (uint64_t) K * N, BK);
     if (rc) return rc;
     g.kind = kKindGroupedRows; g.a_mn = 0; g.b_mn = trans_b ? 0 : 1;
-    g.idesc = make_idesc(a_dtype, b_dtype, g.a_mn, g.b_mn);
+    g.idesc = make_idesc(a_dtype, b_dtype, g.a_mn, g.b_mn, BN);
     g.M = (int) M_total; g.N = (int) N; g.K = (int) K; g.G = (int) G;
     g.tiles_n = (int) cdiv<int64_t>(N, BN);
     g.group_offs = group_offs;
     g.c = out; g.ldc = ldc; g.c_group_stride = 0;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, out, out_dtype, (uint64_t) N, (uint64_t) M_total, 1, (uint64_t) ldc, 0);
+    if (rc) return rc;
     g.a_scale = a_scale; g.as_m = a_scale_stride_m; g.as_k = a_scale_stride_k;
     g.b_scale = b_scale; g.bs_g = b_scale_stride_g; g.bs_n = b_scale_stride_n; g.bs_k = b_scale_stride_k;
     return launch_gemm(g, mode, out_dtype, num_sms, (cudaStream_t) stream);
@@ -705,21 +904,27 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
     PTB_REQUIRE(lhs && rhs && out && group_offs && lhs_scale && rhs_scale, PTB_ERR_ARG,
                 "grouped_gemm_fp8_variable_k: null pointer");
     PTB_REQUIRE(is_fp8(lhs_dtype) && is_fp8(rhs_dtype), PTB_ERR_ARG, "grouped_gemm_fp8_variable_k: operands must be FP8");
+    PTB_REQUIRE(G <= kMaxGroups, PTB_ERR_TOO_LARGE, "grouped_gemm_fp8_variable_k: at most %d groups", kMaxGroups);
     PTB_REQUIRE(rows < (1ll << 31) && OUT_M < (1ll << 31) && OUT_N < (1ll << 31) &&
-                    G * cdiv<int64_t>(OUT_M, BM) * cdiv<int64_t>(OUT_N, BN) < (1ll << 31),
+                    G * cdiv<int64_t>(OUT_M, BM) * cdiv<int64_t>(OUT_N, 128) < (1ll << 31),
                 PTB_ERR_TOO_LARGE, "grouped_gemm_fp8_variable_k: problem too large");
     GemmArgs g{};
+    const int BN = choose_bn(mode);
+    g.bn         = BN;
     const uint64_t r = rows > 0 ? (uint64_t) rows : 1;
     rc = make_map(&g.tm_a, lhs, (uint64_t) OUT_M, r, 1, (uint64_t) ld_lhs, (uint64_t) ld_lhs * r, BK);
     if (rc) return rc;
     rc = make_map(&g.tm_b, rhs, (uint64_t) OUT_N, r, 1, (uint64_t) ld_rhs, (uint64_t) ld_rhs * r, BK);
     if (rc) return rc;
     g.kind = kKindGroupedK; g.a_mn = 1; g.b_mn = 1;
-    g.idesc = make_idesc(lhs_dtype, rhs_dtype, 1, 1);
+    g.idesc = make_idesc(lhs_dtype, rhs_dtype, 1, 1, BN);
     g.M = (int) OUT_M; g.N = (int) OUT_N; g.K = (int) rows; g.G = (int) G;
     g.tiles_n = (int) cdiv<int64_t>(OUT_N, BN);
     g.group_offs = group_offs;
     g.c = out; g.ldc = OUT_N; g.c_group_stride = OUT_M * OUT_N;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, out, out_dtype, (uint64_t) OUT_N, (uint64_t) OUT_M, (uint64_t) G,
+                    (uint64_t) OUT_N, (uint64_t) (OUT_M * OUT_N));
+    if (rc) return rc;
     g.a_scale = lhs_scale; g.as_m = 1; g.as_k = OUT_M;
     g.b_scale = rhs_scale; g.bs_g = 0; g.bs_n = 1; g.bs_k = OUT_N;
     return launch_gemm(g, mode, out_dtype, num_sms, (cudaStream_t) stream);

@@ -76,71 +76,124 @@ struct BlockQuantArgs {
     // segment mode
     int64_t G;
     const int64_t *group_offs;
-    int64_t *var_k_lens;
-    int64_t *var_k_offs;
+    const int64_t *var_k_offs; // padded offsets, written by segment_offsets_kernel before the tile kernel runs
 };
 
+template <typename T> struct Packed2;
+template <> struct Packed2<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    static __device__ __forceinline__ type zero() { return __floats2bfloat162_rn(0.f, 0.f); }
+};
+template <> struct Packed2<__half> {
+    using type = __half2;
+    static __device__ __forceinline__ type zero() { return __floats2half2_rn(0.f, 0.f); }
+};
+template <> struct Packed2<float> {
+    using type = float2;
+    static __device__ __forceinline__ type zero() { return make_float2(0.f, 0.f); }
+};
+
+// One 8-element row fragment kept in its storage format: 16 bytes for 16-bit inputs, so a thread's
+// 8x8 share of the tile costs 32 registers and is decoded on the fly in each pass.
+template <typename T> struct RowFrag {
+    uint4 raw;
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void load(const T *row, int64_t col, int64_t ncols, bool vec) {
+        if (vec && col + 8 <= ncols) {
+            raw = *reinterpret_cast<const uint4 *>(row + col);
+        } else {
+            T e[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = (col + i < ncols) ? row[col + i] : from_f32<T>(0.0f);
+            raw = *reinterpret_cast<const uint4 *>(e);
+        }
+    }
+    __device__ __forceinline__ void decode(float (&v)[8]) const {
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = to_f32(e[i]);
+    }
+};
+template <> struct RowFrag<float> {
+    float4 lo, hi;
+    __device__ __forceinline__ void zero() { lo = hi = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void load(const float *row, int64_t col, int64_t ncols, bool vec) {
+        float v[8];
+        load8<float>(row, col, ncols, vec, v);
+        lo = make_float4(v[0], v[1], v[2], v[3]);
+        hi = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    __device__ __forceinline__ void decode(float (&v)[8]) const {
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+        v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    }
+};
+
+// var_k_lens[g] = ceil(len_g / 128) * 128 and its exclusive prefix var_k_offs[G+1] (one CTA).
+__global__ void __launch_bounds__(256) segment_offsets_kernel(const int64_t *__restrict__ group_offs, int64_t G,
+                                                               int64_t *__restrict__ var_k_lens,
+                                                               int64_t *__restrict__ var_k_offs) {
+    __shared__ int64_t s_scan[256];
+    const int tid     = threadIdx.x;
+    const int64_t per = cdiv<int64_t>(G, 256);
+    const int64_t g0 = (int64_t) tid * per, g1 = imin(g0 + per, G);
+    int64_t local = 0;
+    for (int64_t g = g0; g < g1; ++g) local += cdiv<int64_t>(group_offs[g + 1] - group_offs[g], kBlk) * kBlk;
+    s_scan[tid] = local;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+        int64_t add = (tid >= off) ? s_scan[tid - off] : 0;
+        __syncthreads();
+        s_scan[tid] += add;
+        __syncthreads();
+    }
+    int64_t run = s_scan[tid] - local;
+    for (int64_t g = g0; g < g1; ++g) {
+        const int64_t pl = cdiv<int64_t>(group_offs[g + 1] - group_offs[g], kBlk) * kBlk;
+        var_k_lens[g]    = pl;
+        var_k_offs[g]    = run;
+        run += pl;
+    }
+    if (tid == 255) var_k_offs[G] = s_scan[255];
+}
+
+// Grid: one CTA per 128x128 tile, column tiles fastest, so that CTAs resident together stream whole
+// contiguous row bands (DRAM pages are used end to end instead of 256 bytes at a time).
 template <typename T, int FMT, int MODE, bool SEGMENT>
-__global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p) {
+__global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArgs p) {
     __shared__ float s_colmax[16][kBlk + 1];
     __shared__ float s_colscale[kBlk];
     __shared__ float s_red[8];
-    __shared__ int64_t s_seg[4]; // found, orig_start, orig_end, unused
-    __shared__ int64_t s_scan[256];
+    __shared__ int64_t s_seg[3]; // found, first source row, end of the group's source rows
 
     const int tid = threadIdx.x;
     const int tx  = tid & 15;  // 8-column fragment index inside the tile
     const int ty  = tid >> 4;  // row lane 0..15
+    const int64_t tiles_n = cdiv<int64_t>(p.N, kBlk);
     const int64_t tiles_m = cdiv<int64_t>(SEGMENT ? (p.M + p.G * kBlk) : p.M, kBlk);
-    const int64_t b       = SEGMENT ? 0 : (int64_t) blockIdx.x / tiles_m;
-    const int64_t tm      = SEGMENT ? (int64_t) blockIdx.x : (int64_t) blockIdx.x % tiles_m;
-    const int64_t tn      = blockIdx.y;
+    const int64_t tile    = blockIdx.x;
+    const int64_t tn      = tile % tiles_n;
+    const int64_t tmb     = tile / tiles_n;
+    const int64_t b       = SEGMENT ? 0 : tmb / tiles_m;
+    const int64_t tm      = SEGMENT ? tmb : tmb % tiles_m;
 
     int64_t in_row0  = tm * kBlk; // first source row of this tile
     int64_t in_end   = p.M;       // first invalid source row
     const int64_t out_row0 = tm * kBlk;
 
     if constexpr (SEGMENT) {
-        // Locate the group whose padded segment holds this tile.  Thread t owns a contiguous
-        // chunk of groups; a block-wide scan of the chunk totals gives each chunk's padded start.
-        const int64_t per = cdiv<int64_t>(p.G, 256);
-        const int64_t g0  = (int64_t) tid * per;
-        const int64_t g1  = min(g0 + per, p.G);
-        int64_t local = 0;
-        for (int64_t g = g0; g < g1; ++g) {
-            int64_t len = p.group_offs[g + 1] - p.group_offs[g];
-            local += cdiv<int64_t>(len, kBlk) * kBlk;
-        }
-        s_scan[tid] = local;
+        // find the group whose padded segment [var_k_offs[g], var_k_offs[g+1]) holds this tile
+        const int64_t block_start = tm * kBlk;
         if (tid == 0) s_seg[0] = 0;
         __syncthreads();
-        // exclusive prefix over 256 chunk totals (serial in one warp's worth of steps is plenty:
-        // 8 rounds of Hillis-Steele)
-        for (int off = 1; off < 256; off <<= 1) {
-            int64_t add = (tid >= off) ? s_scan[tid - off] : 0;
-            __syncthreads();
-            s_scan[tid] += add;
-            __syncthreads();
-        }
-        int64_t run = s_scan[tid] - local; // padded start of this thread's first group
-        const bool writer = (blockIdx.x == 0 && blockIdx.y == 0);
-        const int64_t block_start = tm * kBlk;
-        for (int64_t g = g0; g < g1; ++g) {
-            int64_t lo = p.group_offs[g], hi = p.group_offs[g + 1];
-            int64_t pl = cdiv<int64_t>(hi - lo, kBlk) * kBlk;
-            if (writer) {
-                p.var_k_lens[g] = pl;
-                p.var_k_offs[g] = run;
-                if (g == p.G - 1) p.var_k_offs[p.G] = run + pl;
-            }
-            if (block_start >= run && block_start < run + pl) {
+        for (int64_t g = tid; g < p.G; g += 256) {
+            const int64_t ps = p.var_k_offs[g], pe = p.var_k_offs[g + 1];
+            if (block_start >= ps && block_start < pe) {
                 s_seg[0] = 1;
-                s_seg[1] = lo + (block_start - run);
-                s_seg[2] = hi;
+                s_seg[1] = p.group_offs[g] + (block_start - ps);
+                s_seg[2] = p.group_offs[g + 1];
             }
-            run += pl;
         }
-        if (writer && p.G == 0 && tid == 0) p.var_k_offs[0] = 0;
         __syncthreads();
         if (s_seg[0] == 0) return; // tile lies beyond the last padded segment
         in_row0 = s_seg[1];
@@ -152,7 +205,7 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p
     const bool vec_in  = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15u) == 0);
     const bool vec_out = (p.N % 8 == 0);
 
-    float v[8][8];
+    RowFrag<T> frag[8];
     float rmax[8];
     float cmax[8];
 #pragma unroll
@@ -160,20 +213,46 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int64_t r = in_row0 + ty + 16 * i;
-        if (r < in_end && col < p.N) {
-            load8<T>(xb + r * p.N, col, p.N, vec_in, v[i]);
-        } else {
+        if (r < in_end && col < p.N) frag[i].load(xb + r * p.N, col, p.N, vec_in);
+        else frag[i].zero();
+    }
+    if constexpr (sizeof(T) == 2) {
+        // |x| and max are exact in the storage format, so reduce two elements per instruction there
+        using T2 = typename Packed2<T>::type;
+        T2 cm2[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
-        }
-        float m = 0.0f;
+        for (int w = 0; w < 4; ++w) cm2[w] = Packed2<T>::zero();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float a = fabsf(v[i][j]);
-            m       = fmaxf(m, a);
-            cmax[j] = fmaxf(cmax[j], a);
+        for (int i = 0; i < 8; ++i) {
+            const T2 *e = reinterpret_cast<const T2 *>(&frag[i].raw);
+            T2 a[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                a[w] = __habs2(e[w]);
+                if constexpr (MODE & kModeCol) cm2[w] = __hmax2(cm2[w], a[w]);
+            }
+            const T2 m2 = __hmax2(__hmax2(a[0], a[1]), __hmax2(a[2], a[3]));
+            rmax[i]     = fmaxf(to_f32(m2.x), to_f32(m2.y));
         }
-        rmax[i] = m;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            cmax[2 * w]     = to_f32(cm2[w].x);
+            cmax[2 * w + 1] = to_f32(cm2[w].y);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float v[8];
+            frag[i].decode(v);
+            float m = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float a = fabsf(v[j]);
+                m       = fmaxf(m, a);
+                if constexpr (MODE & kModeCol) cmax[j] = fmaxf(cmax[j], a);
+            }
+            rmax[i] = m;
+        }
     }
 
     // ---- row blocks: 16 lanes share a row ---------------------------------------------------
@@ -190,8 +269,9 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p
             if (r < in_end) {
                 if (col < p.N) {
                     float qv[8];
+                    frag[i].decode(qv);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], sc);
+                    for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(qv[j], sc);
                     store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
                 }
                 if (tx == 0) p.s_row[r * p.s_row_stride_m + tn * p.s_row_stride_nb] = sci;
@@ -225,8 +305,9 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p
             const int64_t r = out_row0 + ty + 16 * i;
             if (r < out_end && col < p.N) {
                 float qv[8];
+                frag[i].decode(qv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], cs[j]);
+                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(qv[j], cs[j]);
                 store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
             }
         }
@@ -251,12 +332,13 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const BlockQuantArgs p
             const int64_t r = in_row0 + ty + 16 * i;
             if (r < in_end && col < p.N) {
                 float qv[8];
+                frag[i].decode(qv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(v[i][j], sc);
+                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(qv[j], sc);
                 store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
             }
         }
-        if (tid == 0) p.s_2d[(b * tiles_m + tm) * gridDim.y + tn] = sci;
+        if (tid == 0) p.s_2d[(b * tiles_m + tm) * tiles_n + tn] = sci;
     }
 }
 
@@ -266,8 +348,8 @@ int launch_block_quant(const BlockQuantArgs &a, int x_dtype, int q_dtype, cudaSt
     const int64_t tiles_m = cdiv<int64_t>(rows, kBlk) * (SEGMENT ? 1 : a.B);
     const int64_t tiles_n = cdiv<int64_t>(a.N, kBlk);
     if (tiles_m == 0 || tiles_n == 0) return 0;
-    PTB_REQUIRE(tiles_n <= 65535 && tiles_m <= 2147483647LL, PTB_ERR_TOO_LARGE, "tile grid too large");
-    dim3 grid((unsigned) tiles_m, (unsigned) tiles_n);
+    PTB_REQUIRE(tiles_n * tiles_m <= 2147483647LL, PTB_ERR_TOO_LARGE, "tile grid too large");
+    const unsigned grid = (unsigned) (tiles_m * tiles_n);
     PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
         (quant_block_kernel<T, FMT, MODE, SEGMENT><<<grid, 256, 0, st>>>(a))));
     PTB_LAUNCH_CHECK("quant_block_kernel");
@@ -647,7 +729,10 @@ int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t
     a.q_row = (uint8_t *) q_row; a.s_row = s_row;
     a.s_row_stride_m = 1; a.s_row_stride_nb = M; // row scales stored [ceil(N/128), M]
     a.q_col = (uint8_t *) q_col_padded; a.s_col = s_col_padded;
-    a.group_offs = group_offs; a.var_k_lens = var_k_lens; a.var_k_offs = var_k_offs;
+    a.group_offs = group_offs; a.var_k_offs = var_k_offs;
+    segment_offsets_kernel<<<1, 256, 0, (cudaStream_t) stream>>>(group_offs, G, var_k_lens, var_k_offs);
+    PTB_LAUNCH_CHECK("segment_offsets_kernel");
+    if (M == 0) return 0;
     return launch_block_quant<kModeRow | kModeCol, true>(a, x_dtype, q_dtype, (cudaStream_t) stream);
 }
 
