@@ -75,6 +75,20 @@ int ptb_quant_fp8_tensorwise_with_scale(const void *x, int x_dtype, int64_t n, c
 int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, void *q,
                           int q_dtype, float *scale_inv, void *workspace, ptb_stream_t stream);
 
+/* Rowwise quantize that allocates nothing and needs no workspace argument.
+ * For hosts that are not allowed to obtain device memory on the library's behalf: an inference or
+ * training runtime that hands a plugin only its input and output buffers and owns every other byte
+ * of the device, or a service that forbids cudaMalloc after start-up because the call stalls the
+ * whole device.  Same arithmetic and outputs as ptb_quant_fp8_rowwise; the column-amax scratch is a
+ * fixed 256 KiB array inside the library, so B*N may not exceed 65536 (PTB_ERR_TOO_LARGE otherwise).
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress) and
+ * should therefore be made before any stream capture starts.  All calls share the one array, which
+ * keeps whatever the previous call left in it (each call clears the part it uses): two calls that
+ * can overlap on the GPU, e.g. on different streams, race and must be ordered by the caller.
+ * No counterpart in the reference. */
+int ptb_quant_fp8_rowwise_noalloc(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N,
+                                  void *q, int q_dtype, float *scale_inv, ptb_stream_t stream);
+
 /* 1-D blockwise (block = 128): axis 1 -> scale_inv [M, ceil(N/128)]; axis 0 -> [ceil(M/128), N].
  * Replaces primus_turbo::quant_fp8_blockwise_impl
  * (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:74-118). */

@@ -34,6 +34,7 @@ _PROTOS = {
     "ptb_quant_fp8_tensorwise": [_P, _I, _L, _P, _I, _P, _P, _P],
     "ptb_quant_fp8_tensorwise_with_scale": [_P, _I, _L, _P, _P, _I, _P, _P],
     "ptb_quant_fp8_rowwise": [_P, _I, _L, _L, _L, _P, _I, _P, _P, _P],
+    "ptb_quant_fp8_rowwise_noalloc": [_P, _I, _L, _L, _L, _P, _I, _P, _P],
     "ptb_quant_fp8_block1d": [_P, _I, _L, _L, _I, _P, _I, _P, _P],
     "ptb_quant_fp8_block1d_dual": [_P, _I, _L, _L, _P, _P, _P, _P, _I, _P],
     "ptb_quant_fp8_block2d": [_P, _I, _L, _L, _L, _P, _I, _P, _P],
@@ -86,7 +87,8 @@ def check(rc: int, what: str) -> None:
 
 
 # kernels enqueued by one successful call of each entry point (memset nodes not counted)
-KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_segment_row_col": 2,
+KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_rowwise_noalloc": 2,
+                    "ptb_quant_fp8_segment_row_col": 2,
                     "ptb_gemm_status": 0}
 launch_count = 0  # running total of kernels this process enqueued through the C ABI
 _event_log = None  # when a dict: name -> [(start_event, stop_event), ...] on the launching stream

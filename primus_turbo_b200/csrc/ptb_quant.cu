@@ -674,6 +674,43 @@ int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int6
     return 0;
 }
 
+// ---- rowwise quantize for callers that may not allocate ------------------------------------------
+// The column-amax scratch of the strided rowwise path lives in this fixed array instead of a
+// caller-provided workspace.  Every GPU that loads the library carries these 256 KiB until exit.
+#define PTB_NOALLOC_MAX_COLUMNS 65536
+static __device__ __align__(256) float g_noalloc_rowwise_scratch[PTB_NOALLOC_MAX_COLUMNS];
+
+// Device address of the array above on the current device.  The array's name is only a host-side
+// handle here, so the address is asked for once per device and remembered.
+static int noalloc_scratch_address(float **out) {
+    static float *address_on_device[64] = {};
+    int dev = -1;
+    PTB_CUDA(cudaGetDevice(&dev));
+    PTB_REQUIRE(dev >= 0 && dev < 64, PTB_ERR_UNSUPPORTED, "quant_rowwise_noalloc: device index %d not supported", dev);
+    if (address_on_device[dev] == nullptr) {
+        float *p = nullptr;
+        PTB_CUDA(cudaGetSymbolAddress((void **) &p, g_noalloc_rowwise_scratch));
+        PTB_REQUIRE(p != nullptr, PTB_ERR_DRIVER, "quant_rowwise_noalloc: scratch array has no device address");
+        address_on_device[dev] = p;
+    }
+    *out = address_on_device[dev];
+    return 0;
+}
+
+int ptb_quant_fp8_rowwise_noalloc(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, void *q, int q_dtype,
+                                  float *scale_inv, ptb_stream_t stream) {
+    PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "quant_rowwise_noalloc: negative size");
+    PTB_REQUIRE(B * N <= (int64_t) PTB_NOALLOC_MAX_COLUMNS, PTB_ERR_TOO_LARGE,
+                "quant_rowwise_noalloc: B*N = %lld scale columns exceed the built-in scratch of %d; use "
+                "ptb_quant_fp8_rowwise with a caller-provided workspace",
+                (long long) (B * N), PTB_NOALLOC_MAX_COLUMNS);
+    float *scratch = nullptr;
+    int rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+    // same kernels as the workspace variant; it clears the B*N scratch words it uses before reducing into them
+    return ptb_quant_fp8_rowwise(x, x_dtype, B, M, N, q, q_dtype, scale_inv, scratch, stream);
+}
+
 int ptb_quant_fp8_block1d(const void *x, int x_dtype, int64_t M, int64_t N, int axis, void *q, int q_dtype,
                           float *scale_inv, ptb_stream_t stream) {
     PTB_REQUIRE(M >= 0 && N >= 0 && (axis == 0 || axis == 1), PTB_ERR_ARG, "quant_block1d: bad size/axis");
