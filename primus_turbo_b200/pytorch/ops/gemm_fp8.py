@@ -30,7 +30,7 @@ from primus_turbo_b200.pytorch.core.quantized_tensor import (
     QuantizedTensorPair,
     check_quantized_tensor,
 )
-from primus_turbo_b200.pytorch.kernels.gemm_impl import gemm_fp8_impl
+from primus_turbo_b200.pytorch.kernels.custom_ops import gemm_fp8_impl
 from primus_turbo_b200.pytorch.ops.quantization import quantize_fp8, quantize_fp8_with_trans
 
 __all__ = ["gemm_fp8"]

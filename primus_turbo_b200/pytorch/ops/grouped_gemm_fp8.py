@@ -26,15 +26,15 @@ from primus_turbo_b200.pytorch.core.quantized_tensor import (
     QuantizedTensorPair,
     check_quantized_tensor,
 )
-from primus_turbo_b200.pytorch.kernels.gemm_impl import (
-    group_offs_from_lens,
+from primus_turbo_b200.pytorch.kernels.custom_ops import (
     grouped_gemm_fp8_impl,
     grouped_gemm_fp8_variable_k_impl,
 )
-from primus_turbo_b200.pytorch.kernels.quantization_impl import (
-    quant_fp8_blockwise_for_weight_impl,
-    quant_fp8_blockwise_segment_m_row_col_impl,
+from primus_turbo_b200.pytorch.kernels.custom_ops import quant_fp8_blockwise_for_weight as quant_fp8_blockwise_for_weight_impl
+from primus_turbo_b200.pytorch.kernels.custom_ops import (
+    quant_fp8_blockwise_segment_m_row_col as quant_fp8_blockwise_segment_m_row_col_impl,
 )
+from primus_turbo_b200.pytorch.kernels.gemm_impl import group_offs_from_lens
 
 __all__ = ["grouped_gemm_fp8"]
 
@@ -67,7 +67,7 @@ class FP8GroupedGemmBlockFunc(torch.autograd.Function):
         a_row, a_col, a_s_row, a_s_col, _, _ = quant_fp8_blockwise_segment_m_row_col_impl(
             _contig(a), dt, config.block_size, group_lens, group_offs
         )
-        b8, b_s = quant_fp8_blockwise_for_weight_impl(b, dt, block_size=config.block_size)
+        b8, b_s = quant_fp8_blockwise_for_weight_impl(b, dt, config.block_size)
         out = grouped_gemm_fp8_impl(
             a_row, b8, a_s_row, b_s, group_lens, group_offs, trans_a=False, trans_b=trans_b, out_dtype=out_dtype,
             granularity=config.granularity.value, num_cu=num_cu,

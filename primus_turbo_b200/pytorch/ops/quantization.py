@@ -7,17 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
-from primus_turbo_b200.pytorch.kernels.quantization_impl import (
-    dequant_fp8_blockwise_for_weight_impl,
-    dequant_fp8_blockwise_impl,
-    dequantize_fp8_rowwise_impl,
-    dequantize_fp8_tensorwise_impl,
-    quant_fp8_blockwise_dual_impl,
-    quant_fp8_blockwise_for_weight_impl,
-    quant_fp8_blockwise_impl,
-    quantize_fp8_rowwise_impl,
-    quantize_fp8_tensorwise_impl,
-)
+from primus_turbo_b200.pytorch.kernels import custom_ops as _ops
 
 __all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8"]
 
@@ -38,17 +28,18 @@ def quantize_fp8(
     128x128 tile (weights), otherwise ``axis`` picks 1x128 (axis 1/-1) or 128x1 (axis 0/-2) blocks.
     """
     if granularity == ScalingGranularity.TENSORWISE:
-        return quantize_fp8_tensorwise_impl(x, out_dtype)
+        return _ops.quantize_fp8_tensorwise(x, out_dtype)
     if granularity == ScalingGranularity.ROWWISE:
         if axis is None:
             raise ValueError("axis must be specified for rowwise FP8 quantization")
-        return quantize_fp8_rowwise_impl(x, out_dtype, axis)
+        assert x.is_contiguous(), "The x tensor must be contiguous."
+        return _ops.quantize_fp8_rowwise(x, out_dtype, axis if axis >= 0 else axis + x.dim())
     if granularity == ScalingGranularity.BLOCKWISE:
         assert block_size is not None, "block_size must be specified for BLOCKWISE quantization"
         if scaling_recipe is not None and scaling_recipe.use_2d_block:
-            return quant_fp8_blockwise_for_weight_impl(x, out_dtype, block_size=block_size)
+            return _ops.quant_fp8_blockwise_for_weight(x, out_dtype, block_size)
         assert axis is not None, "axis must be specified for 1D BLOCKWISE quantization"
-        return quant_fp8_blockwise_impl(x, out_dtype, axis=axis, block_size=block_size)
+        return _ops.quant_fp8_blockwise(x, out_dtype, axis, block_size)
     raise NotImplementedError(f"Unknown granularity {granularity}")
 
 
@@ -64,7 +55,7 @@ def quantize_fp8_with_trans(
     """One read of x -> (row copy, row scales [M, N/128], column copy [M,N], column scales [M/128, N])."""
     if granularity == ScalingGranularity.BLOCKWISE:
         assert block_size is not None, "block_size must be specified for BLOCKWISE quantization"
-        return quant_fp8_blockwise_dual_impl(x, out_dtype, block_size=block_size)
+        return _ops.quant_fp8_blockwise_dual(x, out_dtype, block_size)
     raise NotImplementedError(f"Unknown granularity {granularity}")
 
 
@@ -79,15 +70,15 @@ def dequantize_fp8(
     scaling_recipe: Optional[ScalingRecipe] = None,
 ) -> torch.Tensor:
     if granularity == ScalingGranularity.TENSORWISE:
-        return dequantize_fp8_tensorwise_impl(x, out_dtype, scale_inv)
+        return _ops.dequantize_fp8(x, scale_inv, out_dtype, 1, 0, 0)
     if granularity == ScalingGranularity.ROWWISE:
         if axis is None:
             raise ValueError("axis must be specified for rowwise FP8 de-quantization")
-        return dequantize_fp8_rowwise_impl(x, out_dtype, axis, scale_inv)
+        return _ops.dequantize_fp8(x, scale_inv, out_dtype, 2, axis if axis >= 0 else axis + x.dim(), 0)
     if granularity == ScalingGranularity.BLOCKWISE:
         assert block_size is not None, "block_size must be specified for BLOCKWISE de-quantization"
         if scaling_recipe is not None and scaling_recipe.use_2d_block:
-            return dequant_fp8_blockwise_for_weight_impl(x, scale_inv, out_dtype, block_size)
+            return _ops.dequantize_fp8(x, scale_inv, out_dtype, 4, 0, block_size)
         assert axis is not None, "axis must be specified for 1D BLOCKWISE de-quantization"
-        return dequant_fp8_blockwise_impl(x, scale_inv, out_dtype, axis, block_size)
+        return _ops.dequantize_fp8(x, scale_inv, out_dtype, 3, axis, block_size)
     raise NotImplementedError(f"Unknown granularity {granularity}")

@@ -172,3 +172,15 @@ def test_full_size_properties():
     lo = int(vk_offs[g]) + int(lens[g])
     hi = int(vk_offs[g + 1])
     assert int(q_col[lo:hi].view(torch.uint8).max()) == 0
+
+
+def test_quantize_traces_as_one_graph():
+    """``torch.compile(quantize_fp8, fullgraph=True)`` (reference tests/pytorch/ops/test_quantization.py:43-52):
+    the op is an opaque custom op with a fake kernel, so dynamo captures it without a graph break."""
+    x = randn(gen(77), 128, 512).to(DEV)
+    fn = torch.compile(quantize_fp8, fullgraph=True, backend="eager")
+    q, s = fn(x, E4, G.BLOCKWISE, block_size=128, axis=1)
+    qo, so = O.quant_block1d(x.cpu(), E4, 1)
+    assert_quant_equal(q, s, qo, so)
+    q, s = fn(x, E4, G.TENSORWISE)
+    assert_quant_equal(q, s, *O.quant_tensorwise(x.cpu(), E4))
