@@ -12,7 +12,10 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "_C" / "libptb_b200.so"
+import os
+
+# PTB_LIB_PATH points the binding at another build of the same library (e.g. a tuning build)
+_LIB_PATH = Path(os.environ.get("PTB_LIB_PATH") or Path(__file__).resolve().parent / "_C" / "libptb_b200.so")
 
 # element type codes (include/ptb.h)
 PTB_F32, PTB_F16, PTB_BF16, PTB_E4M3, PTB_E5M2 = 0, 1, 2, 3, 4

@@ -277,7 +277,7 @@ struct __align__(16) SharedCtl {
 template <int SCALE, typename OutT, int BN, int DEEP>
 __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using G_ = Geo<BN, DEEP>;
-    constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes, kBBytes = G_::kBBytes;
+    constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes;
     constexpr int kAccBufs = G_::kAccBufs, kWgCols = G_::kWgCols, kChunks = G_::kChunks;
     constexpr int kCStageBytes = G_::kCStageBytes;
     extern __shared__ uint8_t smem_raw[];
@@ -345,7 +345,10 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
     const int total_tiles    = ctl->total_tiles;
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        // register split between the helper warpgroup and the two promotion warpgroups: the 1-D x 1-D
+        // promotion needs every register it can get, the other modes leave more to the MMA issuer
+        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
             Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
@@ -433,7 +436,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ================= promotion + epilogue warpgroups =================
         const int wg   = (warp - 4) >> 2;         // column half
         const int quad = warp & 3;                // TMEM lane quadrant this warp may read
@@ -463,15 +467,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
         float acc[kWgCols];
         float *cs_buf = &ctl->col_scale[warp - 4][0][0];
 
-        // Scales of a tile's first two contraction blocks are requested while the previous tile is
-        // still being converted and stored, later ones two blocks ahead of their use, so the
-        // global-load latency never sits between a finished partial product and its promotion.
-        struct Pre {
-            const float *a_sp, *b_sp;
-            float sa0, sa1, sb0, sb1;
-        } pre;
-        // column scales (1-D x 1-D blocks) of contraction block `kb` of the tile described by b_sp:
-        // copied straight into this warp's shared buffer of parity kb & 1
+        // column scales (1-D x 1-D blocks) of contraction block `kb`: copied straight into this warp's
+        // shared buffer of parity kb & 1 without passing through registers
         auto fetch_col_scales = [&](const float *b_sp_, int col0_, int kb) {
             float *dst = cs_buf + (kb & 1) * 128;
 #pragma unroll
@@ -481,43 +478,35 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                 else dst[q * 32 + lane] = 0.0f;
             }
         };
-        auto preload = [&](const Tile &tt) {
-            const int gb_   = (args.kind == kKindGroupedRows) ? tt.g : 0;
-            const int col0_ = tt.n0 + wg * kWgCols;
-            const int kbb   = tt.k_row0 / BK;
-            const int segs_ = kPerBlock ? tt.num_kb : 0;
-            pre.a_sp = args.a_scale + (int64_t) min(tt.m0 + row_in_tile, tt.m_end - 1) * args.as_m + (int64_t) kbb * args.as_k;
-            pre.b_sp = args.b_scale;
-            if constexpr (SCALE == kScaleBlock2D) pre.b_sp += (int64_t) gb_ * args.bs_g + (int64_t) (col0_ / 128) * args.bs_n;
-            if constexpr (SCALE == kScaleBlock1D) pre.b_sp += (int64_t) kbb * args.bs_k;
-            pre.sa0 = pre.sa1 = pre.sb0 = pre.sb1 = 0.f;
-            if constexpr (kPerBlock) {
-                if (segs_ > 0) pre.sa0 = pre.a_sp[0];
-                if (segs_ > 1) pre.sa1 = pre.a_sp[args.as_k];
-                if constexpr (SCALE == kScaleBlock2D) {
-                    if (segs_ > 0) pre.sb0 = pre.b_sp[0];
-                    if (segs_ > 1) pre.sb1 = pre.b_sp[args.bs_k];
-                } else if (segs_ > 0) {
-                    fetch_col_scales(pre.b_sp, col0_, 0);
-                }
-            }
-        };
 
-        int ti    = blockIdx.x;
-        bool have = sched.get(ti, t);
-        if (have) preload(t);
-        while (ok && have) {
+        for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
             const int gb      = (args.kind == kKindGroupedRows) ? t.g : 0;
             const int row     = t.m0 + row_in_tile;
             const int col0    = t.n0 + wg * kWgCols;
             const int segs    = kPerBlock ? t.num_kb : (t.num_kb > 0 ? 1 : 0);
+            const int kb_base = t.k_row0 / BK;
 #pragma unroll
             for (int j = 0; j < kWgCols; ++j) acc[j] = 0.0f;
-            const float *a_sp = pre.a_sp, *b_sp = pre.b_sp;
-            float sa0 = pre.sa0, sa1 = pre.sa1, sb0 = pre.sb0, sb1 = pre.sb1;
-            if constexpr (SCALE == kScaleBlock1D) {
-                cp_async_wait_all(); // block 0 column scales requested by preload()
-                __syncwarp();
+
+            // Scales are fetched two contraction blocks ahead of their use so that the global-load
+            // latency never sits between a finished partial product and its promotion.
+            const float *a_sp = args.a_scale + (int64_t) min(row, t.m_end - 1) * args.as_m + (int64_t) kb_base * args.as_k;
+            const float *b_sp = args.b_scale;
+            if constexpr (SCALE == kScaleBlock2D)
+                b_sp += (int64_t) gb * args.bs_g + (int64_t) (col0 / 128) * args.bs_n;
+            if constexpr (SCALE == kScaleBlock1D) b_sp += (int64_t) kb_base * args.bs_k;
+            float sa0 = 0.f, sa1 = 0.f, sb0 = 0.f, sb1 = 0.f;
+            if constexpr (kPerBlock) {
+                if (segs > 0) sa0 = a_sp[0];
+                if (segs > 1) sa1 = a_sp[args.as_k];
+                if constexpr (SCALE == kScaleBlock2D) {
+                    if (segs > 0) sb0 = b_sp[0];
+                    if (segs > 1) sb1 = b_sp[args.bs_k];
+                } else if (segs > 0) {
+                    fetch_col_scales(b_sp, col0, 0);
+                    cp_async_wait_all();
+                    __syncwarp();
+                }
             }
 
             for (int sidx = 0; sidx < segs; ++sidx, ++acc_it) {
@@ -592,12 +581,6 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             }
             if (!ok) break;
 
-            // next tile: decode it and put its first scale loads in flight before the store phase
-            Tile tn;
-            ti += gridDim.x;
-            const bool have_next = sched.get(ti, tn);
-            if (have_next) preload(tn);
-
             // ---- scale (tensorwise / rowwise), convert and store ---------------------------------
             float sa = 1.0f;
             if constexpr (SCALE == kScaleTensor) sa = args.a_scale[0] * args.b_scale[0];
@@ -656,8 +639,6 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                     }
                 }
             }
-            t    = tn;
-            have = have_next;
         }
         if (store_pending && lane == 0) tma_store_wait_all();
         if (!ok && lane == 0) atomicExch(&g_gemm_status, 3);
