@@ -252,7 +252,10 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")  # tiny CPU collective for the routing counts
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     assert E_TOTAL % world == 0 and ROWS % world == 0
     cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
@@ -279,8 +282,11 @@ def run_ours(args):
         if world == 1:
             out = grouped_gemm_fp8(a_in, w, counts_dev, config=cfg)
         else:
+            # the synthetic router's counts live on the host, so the exchange plan (rebuilt every
+            # step, as routing changes every step in training) never waits on the device stream
+            plan = build_exchange_plan(counts_dev, counts_host=counts_here, host_group=host_group)
             out = expert_parallel_apply(
-                a_in, counts_dev, lambda rows, lens: grouped_gemm_fp8(rows, w, lens, config=cfg))
+                a_in, counts_dev, lambda rows, lens: grouped_gemm_fp8(rows, w, lens, config=cfg), plan=plan)
         ga, gw = torch.autograd.grad(out, (a_in, w), gy_in)
         return out, ga, gw
 

@@ -24,24 +24,32 @@ namespace ptb {
 namespace {
 
 constexpr int BM = 128, BK = 128;
-constexpr int kThreads    = 384;
 constexpr int kABytes     = BM * BK;              // 16 KiB
 constexpr int kMaxStages  = 8;
 constexpr int kMaxAccBufs = 4;
 
-// Compile-time geometry of one tile width.  BN = 256: two 256-column TMEM buffers, 3 stages of 48 KiB.
-// BN = 128: four 128-column TMEM buffers (the promotion warps get three K-blocks of slack before the
-// tensor core needs a buffer back) and 5 stages of 32 KiB.
+// Compile-time geometry of one tile width.
+//   BN = 256: eight promotion warps own 128 columns each, two 256-column TMEM buffers, 3 stages of
+//             48 KiB (4 stages without output staging when DEEP).  Used when scales are applied once
+//             per tile (tensorwise / rowwise): the TMEM drain is rare there.
+//   BN = 192: twelve promotion warps own 64 columns each, so a warp's whole slice of a partial product
+//             is fetched in one tensor-memory round trip and the buffer is handed back before any
+//             arithmetic.  Measured slower than BN = 256 (register-starved at 152 per thread); kept
+//             selectable for experiments.
+//   BN = 128: eight promotion warps own 64 columns each, four TMEM buffers (kept for experiments; one
+//             CTA per 128-wide tile is shared-memory-bandwidth bound).
 // DEEP = 1 trades the output staging buffer for one more pipeline stage (plain stores in the epilogue).
 template <int BN, int DEEP> struct Geo {
-    static constexpr int kBBytes      = BN * BK;
+    static constexpr int kSliceCols   = BN == 256 ? 128 : 64;       // columns owned by one promotion warp
+    static constexpr int kEpiWarps    = 4 * (BN / kSliceCols);      // 8, 12, 8
+    static constexpr int kThreads     = 128 + 32 * kEpiWarps;
+    static constexpr int kBBytes      = (BN == 192 ? 256 : BN) * BK; // MN-major B arrives in 128-column boxes
     static constexpr int kStageBytes  = kABytes + kBBytes;
-    static constexpr int kStages      = (BN == 256 ? 3 : 5) + DEEP;
+    static constexpr int kStages      = (BN == 128 ? 5 : 3) + DEEP;
     static constexpr int kAccBufs     = 512 / BN;
-    static constexpr int kWgCols      = BN / 2;             // columns owned by one epilogue warpgroup
-    static constexpr int kChunks      = kWgCols / 32;       // 32-column TMEM loads per partial
-    static constexpr int kWarpCBytes  = 32 * kWgCols * 2;   // staging of one warp's 32-row slab (16-bit out)
-    static constexpr int kCStageBytes = DEEP ? 0 : 8 * kWarpCBytes;
+    static constexpr int kChunks      = kSliceCols / 32;            // 32-column TMEM loads per partial
+    static constexpr int kWarpCBytes  = 32 * kSliceCols * 2;        // staging of one warp's 32-row slab (16-bit out)
+    static constexpr int kCStageBytes = DEEP ? 0 : kEpiWarps * kWarpCBytes;
 };
 constexpr int kMaxGroups  = 1024;                 // tile table entries kept in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
@@ -263,7 +271,7 @@ template <> struct Pack8<float> {
 };
 
 struct __align__(16) SharedCtl {
-    float col_scale[8][2][128]; // [epilogue warp][parity][column]: private to a warp, no cross-warp barrier
+    float col_scale[2048]; // per promotion warp: [parity][slice column], private to the warp (no cross-warp barrier)
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[kMaxAccBufs];
@@ -275,11 +283,11 @@ struct __align__(16) SharedCtl {
 };
 
 template <int SCALE, typename OutT, int BN, int DEEP>
-__global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
+__global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using G_ = Geo<BN, DEEP>;
-    constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes;
-    constexpr int kAccBufs = G_::kAccBufs, kWgCols = G_::kWgCols, kChunks = G_::kChunks;
-    constexpr int kCStageBytes = G_::kCStageBytes;
+    constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes, kThreads = G_::kThreads;
+    constexpr int kAccBufs = G_::kAccBufs, kWgCols = G_::kSliceCols, kChunks = G_::kChunks;
+    constexpr int kCStageBytes = G_::kCStageBytes, kEpiWarps = G_::kEpiWarps;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t *smem  = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -298,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
         }
         for (int b = 0; b < kAccBufs; ++b) {
             mbar_init(smem_u32(&ctl->tmem_full[b]), 1);
-            mbar_init(smem_u32(&ctl->tmem_empty[b]), 8); // one arrival per epilogue warp
+            mbar_init(smem_u32(&ctl->tmem_empty[b]), kEpiWarps); // one arrival per promotion warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -347,7 +355,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
     if (warp < 4) {
         // register split between the helper warpgroup and the two promotion warpgroups: the 1-D x 1-D
         // promotion needs every register it can get, the other modes leave more to the MMA issuer
-        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if constexpr (kEpiWarps == 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        else if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
@@ -362,14 +371,14 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                     const uint32_t ph = (it / kStages) & 1;
                     if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1)) { ok = false; break; }
                     const uint32_t full = smem_u32(&ctl->full[s]);
-                    mbar_expect_tx(full, kStageBytes);
+                    mbar_expect_tx(full, kABytes + ((BN == 192 && !args.b_mn) ? BN * BK : G_::kBBytes));
                     const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kABytes;
                     const int k = t.k_row0 + kb * BK;
                     if (args.a_mn) tma_load_3d(sa, &args.tm_a, full, t.m0, k, 0);
                     else           tma_load_3d(sa, &args.tm_a, full, k, t.m0, 0);
                     if (args.b_mn) {
                         tma_load_3d(sb, &args.tm_b, full, t.n0, k, gb);
-                        if constexpr (BN == 256) tma_load_3d(sb + 16384, &args.tm_b, full, t.n0 + 128, k, gb);
+                        if constexpr (BN >= 192) tma_load_3d(sb + 16384, &args.tm_b, full, t.n0 + 128, k, gb);
                     } else {
                         tma_load_3d(sb, &args.tm_b, full, k, t.n0, gb);
                     }
@@ -436,10 +445,11 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
         }
     } else {
-        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if constexpr (kEpiWarps == 12) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        else if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ================= promotion + epilogue warpgroups =================
-        const int wg   = (warp - 4) >> 2;         // column half
+        const int wg   = (warp - 4) >> 2;         // column slice of the tile this warp owns
         const int quad = warp & 3;                // TMEM lane quadrant this warp may read
         const int row_in_tile = quad * 32 + lane;
             OutT *cbase           = reinterpret_cast<OutT *>(args.c);
@@ -448,8 +458,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
             // zero the rows past the last group (output is allocated for M rows)
             const int64_t first = args.group_offs[args.G];
             const int64_t nvec  = (int64_t) (args.M - first) * args.N;
-            const int64_t e0    = (int64_t) blockIdx.x * 256 + (threadIdx.x - 128);
-            for (int64_t e = e0; e < nvec; e += (int64_t) gridDim.x * 256) {
+            const int64_t e0    = (int64_t) blockIdx.x * (32 * kEpiWarps) + (threadIdx.x - 128);
+            for (int64_t e = e0; e < nvec; e += (int64_t) gridDim.x * (32 * kEpiWarps)) {
                 const int64_t r = first + e / args.N, c = e % args.N;
                 cbase[r * args.ldc + c] = from_f32<OutT>(0.0f);
             }
@@ -465,12 +475,12 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
         uint8_t *my_stage     = c_stage + (warp - 4) * G_::kWarpCBytes;
         bool store_pending    = false;
         float acc[kWgCols];
-        float *cs_buf = &ctl->col_scale[warp - 4][0][0];
+        float *cs_buf = &ctl->col_scale[(warp - 4) * 2 * kWgCols];
 
         // column scales (1-D x 1-D blocks) of contraction block `kb`: copied straight into this warp's
         // shared buffer of parity kb & 1 without passing through registers
         auto fetch_col_scales = [&](const float *b_sp_, int col0_, int kb) {
-            float *dst = cs_buf + (kb & 1) * 128;
+            float *dst = cs_buf + (kb & 1) * kWgCols;
 #pragma unroll
             for (int q = 0; q < kChunks; ++q) {
                 const int c = col0_ + q * 32 + lane;
@@ -527,7 +537,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_gemm_kernel(const __grid_cons
                 if (!mbar_wait(smem_u32(&ctl->tmem_full[buf]), (acc_it / kAccBufs) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t) (quad * 32) << 16) + buf * BN + wg * kWgCols;
-                const float *cs      = cs_buf + (sidx & 1) * 128;
+                const float *cs      = cs_buf + (sidx & 1) * kWgCols;
                 const float2 s_row2  = make_float2(s_row, s_row);
                 // two 32-column loads in flight; the second pair is issued while the first is consumed
                 float v0[32], v1[32];
@@ -730,7 +740,8 @@ template <int BN, int DEEP> constexpr size_t smem_bytes() {
     return 1024 + (size_t) Geo<BN, DEEP>::kStages * Geo<BN, DEEP>::kStageBytes + Geo<BN, DEEP>::kCStageBytes +
            sizeof(SharedCtl);
 }
-static_assert(smem_bytes<256, 0>() <= 232448 && smem_bytes<128, 0>() <= 232448 && smem_bytes<256, 1>() <= 232448,
+static_assert(smem_bytes<256, 0>() <= 232448 && smem_bytes<128, 0>() <= 232448 && smem_bytes<256, 1>() <= 232448 &&
+                  smem_bytes<192, 0>() <= 232448,
               "shared memory budget of one CTA exceeded");
 
 template <int SCALE, typename OutT, int BN, int DEEP> int launch_bn(const GemmArgs &args, int grid, cudaStream_t st) {
@@ -743,13 +754,14 @@ template <int SCALE, typename OutT, int BN, int DEEP> int launch_bn(const GemmAr
         PTB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemBytes));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kfn<<<grid, kThreads, kSmemBytes, st>>>(args);
+    kfn<<<grid, Geo<BN, DEEP>::kThreads, kSmemBytes, st>>>(args);
     PTB_LAUNCH_CHECK("fp8_gemm_kernel");
     return 0;
 }
 
 template <int SCALE, typename OutT> int launch_one(const GemmArgs &args, int grid, cudaStream_t st) {
     if (args.bn == 128) return launch_bn<SCALE, OutT, 128, 0>(args, grid, st);
+    if (args.bn == 192) return launch_bn<SCALE, OutT, 192, 0>(args, grid, st);
     return args.deep ? launch_bn<SCALE, OutT, 256, 1>(args, grid, st) : launch_bn<SCALE, OutT, 256, 0>(args, grid, st);
 }
 
@@ -780,15 +792,17 @@ int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cuda
     }
 }
 
-// Tile width.  PTB_GEMM_BN=128|256 overrides (tuning experiments).
+// Tile width.  PTB_GEMM_BN=128|192|256 overrides (tuning experiments).
 int choose_bn(int scale_mode) {
     const char *e = getenv("PTB_GEMM_BN");
     if (e) {
         const int v = atoi(e);
-        if (v == 128 || v == 256) return v;
+        if (v == 128 || v == 192 || v == 256) return v;
     }
+    // Measured on 8192^3 blockwise: 256-wide 2044 TFLOP/s, 192-wide with twelve promotion warps 1558,
+    // 128-wide 1349 -- the narrower geometries stay selectable for experiments only.
     (void) scale_mode;
-    return 256; // the 128-wide tile is shared-memory-bandwidth bound with one CTA per tile (measured)
+    return 256;
 }
 
 int scale_mode_of(int granularity, int b_block_2d, int *mode) {

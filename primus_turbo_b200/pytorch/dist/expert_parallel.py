@@ -37,22 +37,40 @@ class ExchangePlan:
     counts_matrix: torch.Tensor  # [world, E] int64 (device of the payload)
 
 
-def build_exchange_plan(counts_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> ExchangePlan:
-    """One small all-gather of the per-expert counts plus one host read of the split sizes (the
-    all-to-all needs them on the host).  ``counts_local``: int64 ``[E]`` on the payload's device."""
+def build_exchange_plan(
+    counts_local: torch.Tensor,
+    group: Optional[dist.ProcessGroup] = None,
+    counts_host: Optional[torch.Tensor] = None,
+    host_group: Optional[dist.ProcessGroup] = None,
+) -> ExchangePlan:
+    """Derive the exchange from the per-expert row counts of every rank.
+
+    ``counts_local``: int64 ``[E]`` on the payload's device.  The all-to-all needs its split sizes on
+    the host.  By default they are read back from the device (one small all-gather plus one host
+    synchronisation).  A caller that already holds its counts on the host passes ``counts_host``
+    (CPU int64 ``[E]``) and a CPU process group (``host_group``, e.g. gloo): the counts are then
+    gathered on the host and the device stream is never waited on.
+    """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     E = counts_local.numel()
     assert E % world == 0, f"{E} experts cannot be sharded evenly over {world} ranks"
     e_loc = E // world
-    counts_local = counts_local.to(torch.int64).contiguous()
-    flat = torch.empty(world * E, dtype=torch.int64, device=counts_local.device)
-    dist.all_gather_into_tensor(flat, counts_local, group=group)
-    matrix = flat.view(world, E)
-    per_dest = matrix.view(world, world, e_loc).sum(-1)  # [src, dst]
-    host = per_dest.cpu()  # the one host synchronisation of the exchange
-    send_splits = host[rank].tolist()
-    recv_splits = host[:, rank].tolist()
+    dev = counts_local.device
+    if counts_host is not None:
+        assert host_group is not None and not counts_host.is_cuda
+        flat_h = torch.empty(world * E, dtype=torch.int64)
+        dist.all_gather_into_tensor(flat_h, counts_host.to(torch.int64).contiguous(), group=host_group)
+        host_matrix = flat_h.view(world, E)
+        matrix = host_matrix.to(dev, non_blocking=True)
+    else:
+        flat = torch.empty(world * E, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(flat, counts_local.to(torch.int64).contiguous(), group=group)
+        matrix = flat.view(world, E)
+        host_matrix = matrix.cpu()  # the one host synchronisation of the exchange
+    per_dest = host_matrix.view(world, world, e_loc).sum(-1)  # [src, dst]
+    send_splits = per_dest[rank].tolist()
+    recv_splits = per_dest[:, rank].tolist()
     mine = matrix[:, rank * e_loc : (rank + 1) * e_loc]  # [src, e_local] rows arriving per source and expert
     # arrival order is (source, expert); the grouped GEMM wants (expert, source)
     arrive_start = (torch.cumsum(mine.reshape(-1), 0) - mine.reshape(-1)).view(world, e_loc)
@@ -61,7 +79,7 @@ def build_exchange_plan(counts_local: torch.Tensor, group: Optional[dist.Process
     dst_start_es = torch.cumsum(cnt_es, 0) - cnt_es
     total = int(sum(recv_splits))
     gather_index = torch.repeat_interleave(src_start_es - dst_start_es, cnt_es, output_size=total) + torch.arange(
-        total, device=matrix.device
+        total, device=dev
     )
     return ExchangePlan(send_splits, recv_splits, gather_index, mine.sum(0).contiguous(), matrix)
 

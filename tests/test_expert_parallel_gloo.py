@@ -49,6 +49,10 @@ def _worker(rank, store_path, seed, out_q):
 
         plan = build_exchange_plan(counts[rank])
         assert plan.send_splits == counts[rank].view(WORLD, e_loc).sum(1).tolist()
+        # counts already on the host: gathered over a CPU group, same plan
+        plan_h = build_exchange_plan(counts[rank], counts_host=counts[rank], host_group=dist.group.WORLD)
+        assert plan_h.send_splits == plan.send_splits and plan_h.recv_splits == plan.recv_splits
+        assert torch.equal(plan_h.gather_index, plan.gather_index) and torch.equal(plan_h.group_lens, plan.group_lens)
         y = expert_parallel_apply(x, counts[rank], local_fn, plan=plan)
         coeff = torch.arange(y.numel(), dtype=torch.float64).view_as(y) * 1e-2 + 1.0
         (y * coeff).sum().backward()
