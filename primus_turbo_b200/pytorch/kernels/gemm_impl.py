@@ -17,9 +17,7 @@ from primus_turbo_b200._lib import (
     PTB_BLOCKWISE,
     PTB_ROWWISE,
     PTB_TENSORWISE,
-    check,
     dtype_code,
-    lib,
     ptr,
     require_cuda,
     stream_of,
@@ -98,9 +96,11 @@ def gemm_fp8_impl(
     else:
         raise ValueError(f"Unsupported granularity {granularity}")
     with torch.cuda.device(a.device):
-        _lib.call("ptb_gemm_fp8", ptr(a), dtype_code(a.dtype), int(trans_a), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b),
-                b.stride(0), ptr(out), dtype_code(out_dtype), out.stride(0), m, n, k, granularity, ptr(a_s), asm, ask,
-                ptr(b_s), bsn, bsk, b_block_2d, num_sms, stream_of(a))
+        _lib.call(
+            "ptb_gemm_fp8", ptr(a), dtype_code(a.dtype), int(trans_a), a.stride(0), ptr(b),
+            dtype_code(b.dtype), int(trans_b), b.stride(0), ptr(out), dtype_code(out_dtype), out.stride(0), m,
+            n, k, granularity, ptr(a_s), asm, ask, ptr(b_s), bsn, bsk, b_block_2d, num_sms, stream_of(a),
+        )
     return out
 
 
@@ -111,7 +111,9 @@ def group_offs_from_lens(group_lens: torch.Tensor) -> torch.Tensor:
     gl = group_lens.contiguous()
     offs = torch.empty(gl.numel() + 1, dtype=torch.int64, device=gl.device)
     with torch.cuda.device(gl.device):
-        _lib.call("ptb_group_offs", ptr(gl), gl.numel(), ptr(offs), stream_of(gl))
+        _lib.call(
+            "ptb_group_offs", ptr(gl), gl.numel(), ptr(offs), stream_of(gl),
+        )
     return offs
 
 
@@ -156,9 +158,12 @@ def grouped_gemm_fp8_impl(
     else:
         raise ValueError(f"Unsupported granularity {granularity}")
     with torch.cuda.device(a.device):
-        _lib.call("ptb_grouped_gemm_fp8", ptr(a), dtype_code(a.dtype), a.stride(0), ptr(b), dtype_code(b.dtype), int(trans_b), ptr(out),
-                dtype_code(out_dtype), out.stride(0), ptr(group_offs.contiguous()), G, m_total, n, k, granularity,
-                ptr(a_s), asm, ask, ptr(b_s), bsg, bsn, bsk, int(num_cu or 0), stream_of(a))
+        _lib.call(
+            "ptb_grouped_gemm_fp8", ptr(a), dtype_code(a.dtype), a.stride(0), ptr(b), dtype_code(b.dtype),
+            int(trans_b), ptr(out), dtype_code(out_dtype), out.stride(0), ptr(group_offs.contiguous()), G,
+            m_total, n, k, granularity, ptr(a_s), asm, ask, ptr(b_s), bsg, bsn, bsk, int(num_cu or 0),
+            stream_of(a),
+        )
     return out
 
 
@@ -193,9 +198,12 @@ def grouped_gemm_fp8_variable_k_impl(
     elif granularity == PTB_TENSORWISE:
         assert lhs_s.numel() == 1 and rhs_s.numel() == 1
     with torch.cuda.device(lhs.device):
-        _lib.call("ptb_grouped_gemm_fp8_variable_k", ptr(lhs), dtype_code(lhs.dtype), lhs.stride(0), ptr(rhs), dtype_code(rhs.dtype), rhs.stride(0),
-                ptr(out), dtype_code(out_dtype), ptr(group_offs.contiguous()), G, rows, out_m, out_n, granularity,
-                ptr(lhs_s), ptr(rhs_s), int(num_cu or 0), stream_of(lhs))
+        _lib.call(
+            "ptb_grouped_gemm_fp8_variable_k", ptr(lhs), dtype_code(lhs.dtype), lhs.stride(0), ptr(rhs),
+            dtype_code(rhs.dtype), rhs.stride(0), ptr(out), dtype_code(out_dtype),
+            ptr(group_offs.contiguous()), G, rows, out_m, out_n, granularity, ptr(lhs_s), ptr(rhs_s),
+            int(num_cu or 0), stream_of(lhs),
+        )
     return out
 
 

@@ -14,7 +14,7 @@ from typing import Tuple
 import torch
 
 from primus_turbo_b200 import _lib
-from primus_turbo_b200._lib import check, dtype_code, lib, ptr, require_cuda, stream_of
+from primus_turbo_b200._lib import dtype_code, ptr, require_cuda, stream_of
 
 
 def ceil_div(a: int, b: int) -> int:
@@ -37,13 +37,17 @@ def quantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scale:
     with torch.cuda.device(x.device):
         if scale is None:
             ws = torch.empty(_lib.PTB_TENSORWISE_WS_BYTES, dtype=torch.uint8, device=x.device)
-            _lib.call("ptb_quant_fp8_tensorwise", ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(q), dtype_code(out_dtype), ptr(scale_inv), ptr(ws),
-                    stream_of(x))
+            _lib.call(
+                "ptb_quant_fp8_tensorwise", ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(q),
+                dtype_code(out_dtype), ptr(scale_inv), ptr(ws), stream_of(x),
+            )
         else:
             assert scale.numel() == 1, "tensorwise scale must be scalar tensor"
             sc = scale.to(device=x.device, dtype=torch.float32).contiguous()
-            _lib.call("ptb_quant_fp8_tensorwise_with_scale", ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(sc), ptr(q), dtype_code(out_dtype), ptr(scale_inv),
-                    stream_of(x))
+            _lib.call(
+                "ptb_quant_fp8_tensorwise_with_scale", ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(sc),
+                ptr(q), dtype_code(out_dtype), ptr(scale_inv), stream_of(x),
+            )
     return q, scale_inv
 
 
@@ -72,8 +76,10 @@ def quantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int
     scale_inv = torch.empty(sshape, dtype=torch.float32, device=x.device)
     ws = torch.empty(max(B * N, 1), dtype=torch.float32, device=x.device) if N > 1 else None
     with torch.cuda.device(x.device):
-        _lib.call("ptb_quant_fp8_rowwise", ptr(x), dtype_code(x.dtype), B, M, N, ptr(q), dtype_code(out_dtype), ptr(scale_inv), ptr(ws),
-                stream_of(x))
+        _lib.call(
+            "ptb_quant_fp8_rowwise", ptr(x), dtype_code(x.dtype), B, M, N, ptr(q), dtype_code(out_dtype),
+            ptr(scale_inv), ptr(ws), stream_of(x),
+        )
     return q, scale_inv
 
 
@@ -89,7 +95,10 @@ def quant_fp8_blockwise_impl(x: torch.Tensor, dtype: torch.dtype, axis: int, blo
     sshape = (M, ceil_div(N, block_size)) if axis == 1 else (ceil_div(M, block_size), N)
     s = torch.empty(sshape, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("ptb_quant_fp8_block1d", ptr(x), dtype_code(x.dtype), M, N, axis, ptr(q), dtype_code(dtype), ptr(s), stream_of(x))
+        _lib.call(
+            "ptb_quant_fp8_block1d", ptr(x), dtype_code(x.dtype), M, N, axis, ptr(q), dtype_code(dtype),
+            ptr(s), stream_of(x),
+        )
     return q, s
 
 
@@ -104,8 +113,10 @@ def quant_fp8_blockwise_dual_impl(x: torch.Tensor, dtype: torch.dtype, block_siz
     q_col = torch.empty((M, N), dtype=dtype, device=x.device)
     s_col = torch.empty((ceil_div(M, block_size), N), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("ptb_quant_fp8_block1d_dual", ptr(x), dtype_code(x.dtype), M, N, ptr(q_row), ptr(s_row), ptr(q_col), ptr(s_col), dtype_code(dtype),
-                stream_of(x))
+        _lib.call(
+            "ptb_quant_fp8_block1d_dual", ptr(x), dtype_code(x.dtype), M, N, ptr(q_row), ptr(s_row),
+            ptr(q_col), ptr(s_col), dtype_code(dtype), stream_of(x),
+        )
     return q_row, s_row, q_col, s_col
 
 
@@ -125,7 +136,10 @@ def quant_fp8_blockwise_for_weight_impl(w: torch.Tensor, dtype: torch.dtype, blo
     q = torch.empty(w.shape, dtype=dtype, device=w.device)
     s = torch.empty(sshape, dtype=torch.float32, device=w.device)
     with torch.cuda.device(w.device):
-        _lib.call("ptb_quant_fp8_block2d", ptr(w), dtype_code(w.dtype), B, M, N, ptr(q), dtype_code(dtype), ptr(s), stream_of(w))
+        _lib.call(
+            "ptb_quant_fp8_block2d", ptr(w), dtype_code(w.dtype), B, M, N, ptr(q), dtype_code(dtype), ptr(s),
+            stream_of(w),
+        )
     return q, s
 
 
@@ -156,9 +170,11 @@ def quant_fp8_blockwise_segment_m_row_col_impl(
     vk_lens = torch.empty(G, dtype=torch.int64, device=dev)
     vk_offs = torch.empty(G + 1, dtype=torch.int64, device=dev)
     with torch.cuda.device(dev):
-        _lib.call("ptb_quant_fp8_segment_row_col", ptr(x), dtype_code(x.dtype), M, N, G, ptr(group_lens.contiguous()), ptr(group_offs.contiguous()),
-                ptr(q_row), ptr(q_col), ptr(s_row), ptr(s_col), ptr(vk_lens), ptr(vk_offs), dtype_code(dtype),
-                stream_of(x))
+        _lib.call(
+            "ptb_quant_fp8_segment_row_col", ptr(x), dtype_code(x.dtype), M, N, G,
+            ptr(group_lens.contiguous()), ptr(group_offs.contiguous()), ptr(q_row), ptr(q_col), ptr(s_row),
+            ptr(s_col), ptr(vk_lens), ptr(vk_offs), dtype_code(dtype), stream_of(x),
+        )
     return q_row, q_col, s_row, s_col, vk_lens, vk_offs
 
 
@@ -168,8 +184,10 @@ def dequantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scal
     xc = x.contiguous()
     out = torch.empty(xc.shape, dtype=out_dtype, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("ptb_dequant_fp8_tensorwise", ptr(xc), dtype_code(xc.dtype), xc.numel(), ptr(scale_inv.contiguous()), ptr(out),
-                dtype_code(out_dtype), stream_of(x))
+        _lib.call(
+            "ptb_dequant_fp8_tensorwise", ptr(xc), dtype_code(xc.dtype), xc.numel(),
+            ptr(scale_inv.contiguous()), ptr(out), dtype_code(out_dtype), stream_of(x),
+        )
     return out
 
 
@@ -182,7 +200,10 @@ def dequantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: i
     B, M, N = _bmn(tuple(x.shape), ax)
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("ptb_dequant_fp8_rowwise", ptr(x), dtype_code(x.dtype), B, M, N, ptr(scale_inv), ptr(out), dtype_code(out_dtype), stream_of(x))
+        _lib.call(
+            "ptb_dequant_fp8_rowwise", ptr(x), dtype_code(x.dtype), B, M, N, ptr(scale_inv), ptr(out),
+            dtype_code(out_dtype), stream_of(x),
+        )
     return out
 
 
@@ -195,8 +216,10 @@ def dequant_fp8_blockwise_impl(x_fp8, scale_inv, out_dtype, axis: int, block_siz
     M, N = x_fp8.shape
     out = torch.empty((M, N), dtype=out_dtype, device=x_fp8.device)
     with torch.cuda.device(x_fp8.device):
-        _lib.call("ptb_dequant_fp8_block1d", ptr(x_fp8), dtype_code(x_fp8.dtype), M, N, axis, ptr(scale_inv.contiguous()), ptr(out),
-                dtype_code(out_dtype), stream_of(x_fp8))
+        _lib.call(
+            "ptb_dequant_fp8_block1d", ptr(x_fp8), dtype_code(x_fp8.dtype), M, N, axis,
+            ptr(scale_inv.contiguous()), ptr(out), dtype_code(out_dtype), stream_of(x_fp8),
+        )
     return out
 
 
@@ -212,8 +235,10 @@ def dequant_fp8_blockwise_for_weight_impl(w_fp8, scale_inv, out_dtype, block_siz
         B, M, N = w_fp8.shape
     out = torch.empty(w_fp8.shape, dtype=out_dtype, device=w_fp8.device)
     with torch.cuda.device(w_fp8.device):
-        _lib.call("ptb_dequant_fp8_block2d", ptr(w_fp8), dtype_code(w_fp8.dtype), B, M, N, ptr(scale_inv.contiguous()), ptr(out),
-                dtype_code(out_dtype), stream_of(w_fp8))
+        _lib.call(
+            "ptb_dequant_fp8_block2d", ptr(w_fp8), dtype_code(w_fp8.dtype), B, M, N,
+            ptr(scale_inv.contiguous()), ptr(out), dtype_code(out_dtype), stream_of(w_fp8),
+        )
     return out
 
 
@@ -226,5 +251,7 @@ def transpose_2d_fp8(x: torch.Tensor) -> torch.Tensor:
     B = xc.numel() // max(M * N, 1) if M * N else 0
     out = torch.empty((*xc.shape[:-2], N, M), dtype=xc.dtype, device=xc.device)
     with torch.cuda.device(x.device):
-        _lib.call("ptb_transpose_2d_u8", ptr(xc), B, M, N, ptr(out), stream_of(x))
+        _lib.call(
+            "ptb_transpose_2d_u8", ptr(xc), B, M, N, ptr(out), stream_of(x),
+        )
     return out
