@@ -51,6 +51,11 @@ template <int BN, int DEEP> struct Geo {
     static constexpr int kWarpCBytes  = 32 * kSliceCols * 2;        // staging of one warp's 32-row slab (16-bit out)
     static constexpr int kCStageBytes = DEEP ? 0 : kEpiWarps * kWarpCBytes;
 };
+// Block scales reach the promotion warps through a shared-memory ring filled by a loader warp
+// several contraction blocks ahead: one slot holds the 128 row scales of the tile's rows and up to
+// 256 column scales (1-D x 1-D blocks) or one scale per column slice (1-D x 2-D blocks).
+constexpr int kScaleSlots = 4;
+constexpr int kSlotFloats = 128 + 256;
 constexpr int kMaxGroups  = 1024;                 // tile table entries kept in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
 
@@ -132,6 +137,10 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t src
                  "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
+// pulls a tensor map into the descriptor cache before the first copy that uses it
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *tm) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -140,7 +149,17 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void cp_async_f32(float *dst_smem, const float *src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
+// same, writing 0.0f instead when `valid` is false (the source is not read then)
+__device__ __forceinline__ void cp_async_f32_zfill(float *dst_smem, const float *src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst_smem)), "l"(src),
+                 "r"(valid ? 4u : 0u)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// the barrier receives one arrival from this thread once all of its earlier cp.async copies have landed
+__device__ __forceinline__ void cp_async_arrive_on(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -195,47 +214,93 @@ struct Tile {
     int k_tail;    // variable-K only: valid rows of the last block when the group length is not a multiple of 128, else 0
 };
 
+struct __align__(16) SharedCtl {
+    float scale_ring[kScaleSlots * kSlotFloats]; // per contraction block: 128 row scales, then the column scales
+    uint64_t sc_full[kScaleSlots];
+    uint64_t sc_empty[kScaleSlots];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[kMaxAccBufs];
+    uint64_t tmem_empty[kMaxAccBufs];
+    uint32_t tmem_base;
+    int total_tiles;
+    int sched_q, sched_rem; // grid stride = sched_q * tiles_n + sched_rem
+    int tile_prefix[kMaxGroups + 1];
+    int group_offs[kMaxGroups + 1]; // copy of the device offsets: the schedule never waits on global memory
+};
+
+// Walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one CTA.  The linear index is split
+// into its coordinates once, with divisions, in the constructor; every later tile is reached by
+// adding the (pre-split) grid stride and carrying, because each role warp pays for the walk on its
+// critical path once per tile and short-K tiles (wgrad) last only a few thousand cycles.
 struct Schedule {
     const GemmArgs &a;
-    const int *tile_prefix; // shared: cumulative m-tiles per group (grouped rows) [G+1]
-    const int *offs;        // shared: group offsets [G+1]
-    int total;
-    int cursor_g;
+    const SharedCtl *ctl; // loop invariants are re-read from shared / constant memory instead of held in registers
+    int lin;
+    int p0, p1, p2; // dense: (band, index in band, -); grouped rows: (m-tile, n-tile, group cursor);
+                    // grouped variable-K: (group, m-tile, n-tile)
 
-    __device__ Schedule(const GemmArgs &args, const int *prefix, const int *group_offs, int total_tiles)
-        : a(args), tile_prefix(prefix), offs(group_offs), total(total_tiles), cursor_g(0) {}
-
-    __device__ bool get(int t, Tile &o) {
-        if (t >= total) return false;
+    __device__ Schedule(const GemmArgs &args, const SharedCtl *c) : a(args), ctl(c), lin(blockIdx.x) {
+        p0 = p1 = p2 = 0;
+        if (lin >= ctl->total_tiles) return;
         if (a.kind == kKindDense) {
-            // groups of 8 row-tiles, rows fastest inside a group: neighbouring CTAs share B columns
+            const int band = 8 * a.tiles_n;
+            p0 = lin / band;
+            p1 = lin - p0 * band;
+        } else if (a.kind == kKindGroupedRows) {
+            p0 = lin / a.tiles_n;
+            p1 = lin - p0 * a.tiles_n;
+        } else {
+            const int per_g = ((a.M + BM - 1) / BM) * a.tiles_n;
+            p0          = lin / per_g;
+            const int r = lin - p0 * per_g;
+            p1 = r / a.tiles_n;
+            p2 = r - p1 * a.tiles_n;
+        }
+    }
+
+    // Emits the current tile and steps to the CTA's next one; false when the CTA has no tile left.
+    __device__ bool get(Tile &o) {
+        if (lin >= ctl->total_tiles) return false;
+        const int step = gridDim.x, tiles_m = (a.M + BM - 1) / BM;
+        const int *offs = ctl->group_offs;
+        if (a.kind == kKindDense) {
+            // bands of 8 row-tiles, rows fastest inside a band: neighbouring CTAs share B columns
             // and a narrow band of A rows.
-            const int tiles_m = (a.M + BM - 1) / BM;
-            const int band    = 8 * a.tiles_n;
-            const int gi      = t / band;
-            const int first   = gi * 8;
-            const int rows    = min(8, tiles_m - first);
-            const int r       = t - gi * band;
-            const int mt = first + r % rows, nt = r / rows;
+            int rows;
+            for (;;) {
+                rows = min(8, tiles_m - 8 * p0);
+                const int sz = rows * a.tiles_n;
+                if (p1 < sz) break;
+                p1 -= sz;
+                ++p0;
+            }
+            const int nt = rows == 8 ? (p1 >> 3) : p1 / rows;
+            const int mt = 8 * p0 + (p1 - nt * rows);
             o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * a.bn; o.g = 0; o.k_row0 = 0;
             o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
+            p1 += step;
         } else if (a.kind == kKindGroupedRows) {
-            const int mbi = t / a.tiles_n, nt = t - mbi * a.tiles_n;
-            while (tile_prefix[cursor_g + 1] <= mbi) ++cursor_g;
-            const int g  = cursor_g;
+            const int *tile_prefix = ctl->tile_prefix;
+            while (tile_prefix[p2 + 1] <= p0) ++p2;
+            const int g  = p2;
             const int lo = offs[g], hi = offs[g + 1];
-            o.m0 = lo + (mbi - tile_prefix[g]) * BM; o.m_end = hi; o.n0 = nt * a.bn; o.g = g;
+            o.m0 = lo + (p0 - tile_prefix[g]) * BM; o.m_end = hi; o.n0 = p1 * a.bn; o.g = g;
             o.k_row0 = 0; o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
+            p1 += ctl->sched_rem;
+            p0 += ctl->sched_q;
+            if (p1 >= a.tiles_n) { p1 -= a.tiles_n; ++p0; }
         } else {
-            const int tiles_m = (a.M + BM - 1) / BM;
-            const int per_g   = tiles_m * a.tiles_n;
-            const int g = t / per_g, r = t - g * per_g;
-            const int mt = r / a.tiles_n, nt = r - mt * a.tiles_n;
-            const int lo = offs[g], hi = offs[g + 1];
-            o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * a.bn; o.g = g; o.k_row0 = lo;
+            const int lo = offs[p0], hi = offs[p0 + 1];
+            o.m0 = p1 * BM; o.m_end = a.M; o.n0 = p2 * a.bn; o.g = p0; o.k_row0 = lo;
             o.num_kb = (hi - lo + BK - 1) / BK;
             o.k_tail = (hi - lo) % BK;
+            p2 += ctl->sched_rem;
+            p1 += ctl->sched_q;
+            if (p2 >= a.tiles_n) { p2 -= a.tiles_n; ++p1; }
+            while (p1 >= tiles_m) { p1 -= tiles_m; ++p0; }
         }
+        lin += step;
         return true;
     }
 };
@@ -270,17 +335,6 @@ template <> struct Pack8<float> {
     }
 };
 
-struct __align__(16) SharedCtl {
-    float col_scale[2048]; // per promotion warp: [parity][slice column], private to the warp (no cross-warp barrier)
-    uint64_t full[kMaxStages];
-    uint64_t empty[kMaxStages];
-    uint64_t tmem_full[kMaxAccBufs];
-    uint64_t tmem_empty[kMaxAccBufs];
-    uint32_t tmem_base;
-    int total_tiles;
-    int tile_prefix[kMaxGroups + 1];
-    int group_offs[kMaxGroups + 1]; // copy of the device offsets: the schedule never waits on global memory
-};
 
 template <int SCALE, typename OutT, int BN, int DEEP>
 __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
@@ -308,8 +362,21 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
             mbar_init(smem_u32(&ctl->tmem_full[b]), 1);
             mbar_init(smem_u32(&ctl->tmem_empty[b]), kEpiWarps); // one arrival per promotion warp
         }
+        for (int b = 0; b < kScaleSlots; ++b) {
+            mbar_init(smem_u32(&ctl->sc_full[b]), 32);         // every loader lane, after its own copies
+            mbar_init(smem_u32(&ctl->sc_empty[b]), kEpiWarps); // one arrival per promotion warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (threadIdx.x == 64) {
+        tma_prefetch_map(&args.tm_a);
+        tma_prefetch_map(&args.tm_b);
+        if (args.use_tma_store) tma_prefetch_map(&args.tm_c);
+    }
+    if (threadIdx.x == 32) {
+        ctl->sched_q   = (int) gridDim.x / args.tiles_n;
+        ctl->sched_rem = (int) gridDim.x % args.tiles_n;
     }
     if (args.kind != kKindDense) {
         for (int g = threadIdx.x; g <= args.G; g += kThreads) ctl->group_offs[g] = (int) args.group_offs[g];
@@ -350,7 +417,6 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
-    const int total_tiles    = ctl->total_tiles;
 
     if (warp < 4) {
         // register split between the helper warpgroup and the two promotion warpgroups: the 1-D x 1-D
@@ -360,11 +426,11 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
-            Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
+            Schedule sched(args, ctl);
             Tile t;
             uint32_t it = 0; // ring position over the whole kernel
             bool ok     = true;
-            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+            while (ok && sched.get(t)) {
                 const int gb = (args.kind == kKindGroupedRows) ? t.g : 0;
                 for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
                     const int s = it % kStages;
@@ -395,14 +461,14 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
             }
         } else if (warp == 1) {
             // ================= MMA issuer (whole warp walks the schedule, lane 0 issues) =================
-            Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
+            Schedule sched(args, ctl);
             Tile t;
             uint32_t it = 0, acc_it = 0;
             bool ok     = true;
             const uint32_t a_lbo = 0, a_sbo = 1024, a_step = args.a_mn ? 4096u : 32u;
             const uint32_t b_lbo = args.b_mn ? 16384u : 0u, b_sbo = 1024;
             const uint32_t b_step = args.b_mn ? 4096u : 32u;
-            for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+            while (ok && sched.get(t)) {
                 for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -443,6 +509,43 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 }
             }
             if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
+        } else if (warp == 3) {
+            // ================= scale loader (1-D x 1-D block scales) =================
+            // Copies each contraction block's row and column scales into the ring with cp.async; the
+            // slot's barrier hears from every lane when that lane's copies have landed, so neither this
+            // warp nor the promotion warps ever hold a register waiting on a scale load from global
+            // memory.  (With 1-D x 2-D blocks a thread needs two scalars per block and fetches them
+            // itself two blocks ahead: measured faster than a ring there.)
+            if constexpr (SCALE == kScaleBlock1D) {
+                Schedule sched(args, ctl);
+                Tile t;
+                uint32_t it = 0;
+                bool ok     = true;
+                while (ok && sched.get(t)) {
+                    const int kb_base = t.k_row0 / BK;
+                    for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+                        const int slot = it % kScaleSlots;
+                        if (!mbar_wait(smem_u32(&ctl->sc_empty[slot]), ((it / kScaleSlots) & 1) ^ 1)) { ok = false; break; }
+                        float *dst         = &ctl->scale_ring[slot * kSlotFloats];
+                        const float *a_src = args.a_scale + (int64_t) (kb_base + kb) * args.as_k;
+#pragma unroll
+                        for (int i = 0; i < BM / 32; ++i) {
+                            const int r = min(t.m0 + i * 32 + lane, t.m_end - 1); // rows past the group are never stored
+                            cp_async_f32(dst + i * 32 + lane, a_src + (int64_t) r * args.as_m);
+                        }
+                        const float *b_src = args.b_scale + (int64_t) (kb_base + kb) * args.bs_k;
+#pragma unroll
+                        for (int i = 0; i < BN / 32; ++i) {
+                            const int c = t.n0 + i * 32 + lane;
+                            cp_async_f32_zfill(dst + 128 + i * 32 + lane, b_src + (int64_t) min(c, args.N - 1) * args.bs_n,
+                                               c < args.N);
+                        }
+                        cp_async_arrive_on(smem_u32(&ctl->sc_full[slot]));
+                    }
+                }
+                cp_async_wait_all(); // nothing of this warp's is in flight when the CTA tears down
+                if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
+            }
         }
     } else {
         if constexpr (kEpiWarps == 12) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
@@ -465,7 +568,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
             }
         }
 
-        Schedule sched(args, ctl->tile_prefix, ctl->group_offs, total_tiles);
+        Schedule sched(args, ctl);
         Tile t;
         uint32_t acc_it = 0;
         bool ok         = true;
@@ -475,69 +578,49 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         uint8_t *my_stage     = c_stage + (warp - 4) * G_::kWarpCBytes;
         bool store_pending    = false;
         float acc[kWgCols];
-        float *cs_buf = &ctl->col_scale[(warp - 4) * 2 * kWgCols];
-
-        // column scales (1-D x 1-D blocks) of contraction block `kb`: copied straight into this warp's
-        // shared buffer of parity kb & 1 without passing through registers
-        auto fetch_col_scales = [&](const float *b_sp_, int col0_, int kb) {
-            float *dst = cs_buf + (kb & 1) * kWgCols;
-#pragma unroll
-            for (int q = 0; q < kChunks; ++q) {
-                const int c = col0_ + q * 32 + lane;
-                if (c < args.N) cp_async_f32(dst + q * 32 + lane, b_sp_ + (int64_t) c * args.bs_n + (int64_t) kb * args.bs_k);
-                else dst[q * 32 + lane] = 0.0f;
-            }
-        };
-
-        for (int ti = blockIdx.x; ok && sched.get(ti, t); ti += gridDim.x) {
+        while (ok && sched.get(t)) {
             const int gb      = (args.kind == kKindGroupedRows) ? t.g : 0;
             const int row     = t.m0 + row_in_tile;
             const int col0    = t.n0 + wg * kWgCols;
             const int segs    = kPerBlock ? t.num_kb : (t.num_kb > 0 ? 1 : 0);
-            const int kb_base = t.k_row0 / BK;
 #pragma unroll
             for (int j = 0; j < kWgCols; ++j) acc[j] = 0.0f;
 
-            // Scales are fetched two contraction blocks ahead of their use so that the global-load
-            // latency never sits between a finished partial product and its promotion.
-            const float *a_sp = args.a_scale + (int64_t) min(row, t.m_end - 1) * args.as_m + (int64_t) kb_base * args.as_k;
-            const float *b_sp = args.b_scale;
-            if constexpr (SCALE == kScaleBlock2D)
-                b_sp += (int64_t) gb * args.bs_g + (int64_t) (col0 / 128) * args.bs_n;
-            if constexpr (SCALE == kScaleBlock1D) b_sp += (int64_t) kb_base * args.bs_k;
+            // 1-D x 2-D block scales: each thread fetches its two scalars two contraction blocks
+            // ahead of their use
+            const float *a_sp = nullptr, *b_sp = nullptr;
             float sa0 = 0.f, sa1 = 0.f, sb0 = 0.f, sb1 = 0.f;
-            if constexpr (kPerBlock) {
-                if (segs > 0) sa0 = a_sp[0];
-                if (segs > 1) sa1 = a_sp[args.as_k];
-                if constexpr (SCALE == kScaleBlock2D) {
-                    if (segs > 0) sb0 = b_sp[0];
-                    if (segs > 1) sb1 = b_sp[args.bs_k];
-                } else if (segs > 0) {
-                    fetch_col_scales(b_sp, col0, 0);
-                    cp_async_wait_all();
-                    __syncwarp();
-                }
+            if constexpr (SCALE == kScaleBlock2D) {
+                a_sp = args.a_scale + (int64_t) min(row, t.m_end - 1) * args.as_m;
+                b_sp = args.b_scale + (int64_t) gb * args.bs_g + (int64_t) min(col0 / 128, (args.N - 1) / 128) * args.bs_n;
+                if (segs > 0) { sa0 = a_sp[0]; sb0 = b_sp[0]; }
+                if (segs > 1) { sa1 = a_sp[args.as_k]; sb1 = b_sp[args.bs_k]; }
             }
 
             for (int sidx = 0; sidx < segs; ++sidx, ++acc_it) {
                 const uint32_t buf = acc_it % kAccBufs;
                 float s_row        = 1.0f;
-                if constexpr (kPerBlock) {
-                    s_row = (SCALE == kScaleBlock2D) ? sa0 * sb0 : sa0;
+                const float *cs    = nullptr;
+                const int slot     = acc_it % kScaleSlots;
+                if constexpr (SCALE == kScaleBlock1D) {
+                    // this block's scales were copied into the ring by the loader warp, normally long ago
+                    if (!mbar_wait(smem_u32(&ctl->sc_full[slot]), (acc_it / kScaleSlots) & 1)) { ok = false; break; }
+                    const float *sl = &ctl->scale_ring[slot * kSlotFloats];
+                    s_row           = sl[row_in_tile];
+                    cs              = sl + 128 + wg * kWgCols;
+                }
+                if constexpr (SCALE == kScaleBlock2D) {
+                    s_row = sa0 * sb0;
                     sa0   = sa1;
                     sb0   = sb1;
                     if (sidx + 2 < segs) {
                         sa1 = a_sp[(int64_t) (sidx + 2) * args.as_k];
-                        if constexpr (SCALE == kScaleBlock2D) sb1 = b_sp[(int64_t) (sidx + 2) * args.bs_k];
-                    }
-                    if constexpr (SCALE == kScaleBlock1D) {
-                        if (sidx + 1 < segs) fetch_col_scales(b_sp, col0, sidx + 1);
+                        sb1 = b_sp[(int64_t) (sidx + 2) * args.bs_k];
                     }
                 }
                 if (!mbar_wait(smem_u32(&ctl->tmem_full[buf]), (acc_it / kAccBufs) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t) (quad * 32) << 16) + buf * BN + wg * kWgCols;
-                const float *cs      = cs_buf + (sidx & 1) * kWgCols;
                 const float2 s_row2  = make_float2(s_row, s_row);
                 // two 32-column loads in flight; the second pair is issued while the first is consumed
                 float v0[32], v1[32];
@@ -585,8 +668,8 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 }
 #undef PTB_PROMOTE
                 if constexpr (SCALE == kScaleBlock1D) {
-                    cp_async_wait_all(); // next block's column scales have landed
-                    __syncwarp();
+                    __syncwarp(); // every lane has read its scales: the loader may refill the slot
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->sc_empty[slot]));
                 }
             }
             if (!ok) break;
