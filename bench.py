@@ -241,7 +241,8 @@ def run_ours(args):
 
     from primus_turbo_b200 import _lib
     from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity
-    from primus_turbo_b200.pytorch.dist.expert_parallel import build_exchange_plan, expert_parallel_apply
+    from primus_turbo_b200.pytorch.dist.expert_parallel import (
+        build_exchange_plan, ep_grouped_gemm_fp8, expert_parallel_apply)
     from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
 
     if not torch.cuda.is_available():
@@ -254,6 +255,9 @@ def run_ours(args):
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
+        if args.ep_overlap:
+            # the collective that runs beside wgrad must fit on the SMs wgrad leaves free
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.ep_reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
         host_group = dist.new_group(backend="gloo")  # tiny CPU collective for the routing counts
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
@@ -285,8 +289,13 @@ def run_ours(args):
             # the synthetic router's counts live on the host, so the exchange plan (rebuilt every
             # step, as routing changes every step in training) never waits on the device stream
             plan = build_exchange_plan(counts_dev, counts_host=counts_here, host_group=host_group)
-            out = expert_parallel_apply(
-                a_in, counts_dev, lambda rows, lens: grouped_gemm_fp8(rows, w, lens, config=cfg), plan=plan)
+            if args.ep_overlap:
+                # weight quantisation beside the dispatch, wgrad beside the return of grad_a
+                out = ep_grouped_gemm_fp8(a_in, w, counts_dev, config=cfg, plan=plan, overlap=True,
+                                          reserve_sms=args.ep_reserve_sms)
+            else:
+                out = expert_parallel_apply(
+                    a_in, counts_dev, lambda rows, lens: grouped_gemm_fp8(rows, w, lens, config=cfg), plan=plan)
         ga, gw = torch.autograd.grad(out, (a_in, w), gy_in)
         return out, ga, gw
 
@@ -375,6 +384,9 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "fp8_e4m3 operands, fp32 accumulate, bf16 in/out", "data": "synthetic",
             "config": {"workload": WORKLOAD, "experts": E_TOTAL, "experts_per_gpu": e_loc, "hidden": HIDDEN,
                        "n": N_OUT, "routed_rows": ROWS, "parallelism": f"ep{world}",
+                       "ep_overlap": bool(args.ep_overlap) if world > 1 else None,
+                       "load_imbalance_max_over_mean_rows": float(
+                           counts.view(world, -1).sum(1).max().item() * world / counts.sum().item()),
                        "l2": "inputs larger than L2 (7.5 GB of FP8 weights per pass)"},
             "per_gpu_tflops": value / world, "pct_of_fp8_peak_per_gpu": 100.0 * value / world / fp8_peak,
             "fp8_peak_tflops": fp8_peak,
@@ -403,6 +415,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--ep-overlap", type=int, default=0,
+                    help="N > 1: 1 = weight quantise beside the dispatch and wgrad beside the grad_a return "
+                         "(measured slower: both sides of each pair are HBM-bound); 0 = serial")
+    ap.add_argument("--ep-reserve-sms", type=int, default=16, help="SMs wgrad leaves to the overlapped collective")
     ap.add_argument("--experts", type=int, default=E_TOTAL, help="smaller case of the same workload (profiling)")
     ap.add_argument("--rows", type=int, default=ROWS, help="smaller case of the same workload (profiling)")
     args = ap.parse_args()

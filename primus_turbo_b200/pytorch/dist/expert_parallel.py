@@ -23,7 +23,9 @@ from typing import Callable, List, Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["ExchangePlan", "build_exchange_plan", "expert_parallel_apply", "ep_grouped_gemm_fp8"]
+__all__ = [
+    "ExchangePlan", "build_exchange_plan", "expert_parallel_apply", "ep_grouped_gemm_fp8", "BlockwiseLocalSteps",
+]
 
 
 @dataclass
@@ -33,8 +35,47 @@ class ExchangePlan:
     send_splits: List[int]  # rows this rank sends to each destination rank
     recv_splits: List[int]  # rows this rank receives from each source rank
     gather_index: torch.Tensor  # [rows_recv] int64: expert-major row j comes from arrival row gather_index[j]
+    scatter_index: torch.Tensor  # [rows_recv] int64: the inverse permutation (arrival row i is expert-major row scatter_index[i])
     group_lens: torch.Tensor  # [E_local] int64 rows per local expert after the exchange
     counts_matrix: torch.Tensor  # [world, E] int64 (device of the payload)
+
+
+class _PinnedPool:
+    """Page-locked staging buffers for the plan's one host-to-device copy.  A copy from pageable
+    memory makes the host wait for the stream, which would expose every launch of the step; a
+    pinned source does not.  A buffer is reused only after the copy that read it has completed."""
+
+    def __init__(self):
+        self._items = []  # (buffer, event)
+
+    def take(self, numel: int):
+        for i, (buf, ev) in enumerate(self._items):
+            if buf.numel() >= numel and ev.query():
+                return self._items.pop(i)[0]
+        return torch.empty(max(numel, 1 << 16), dtype=torch.int64, pin_memory=True)
+
+    def give_back(self, buf: torch.Tensor, ev):
+        self._items.append((buf, ev))
+        if len(self._items) > 8:
+            self._items.pop(0)
+
+
+_pinned_pool = _PinnedPool()
+
+
+def _plan_from_matrix(matrix: torch.Tensor, rank: int, world: int):
+    """Index arithmetic of the plan on whatever device ``matrix`` ([world, E] int64) lives on."""
+    E = matrix.shape[1]
+    e_loc = E // world
+    dev = matrix.device
+    mine = matrix[:, rank * e_loc : (rank + 1) * e_loc]  # [src, e_local] rows arriving per source and expert
+    # arrival order is (source, expert); the grouped GEMM wants (expert, source)
+    flat = mine.reshape(-1)
+    arrive_start = (torch.cumsum(flat, 0) - flat).view(world, e_loc)
+    cnt_es = mine.t().reshape(-1)  # segments in (expert, source) order
+    src_start_es = arrive_start.t().reshape(-1)
+    dst_start_es = torch.cumsum(cnt_es, 0) - cnt_es
+    return mine, cnt_es, src_start_es - dst_start_es, dev
 
 
 def build_exchange_plan(
@@ -47,9 +88,11 @@ def build_exchange_plan(
 
     ``counts_local``: int64 ``[E]`` on the payload's device.  The all-to-all needs its split sizes on
     the host.  By default they are read back from the device (one small all-gather plus one host
-    synchronisation).  A caller that already holds its counts on the host passes ``counts_host``
-    (CPU int64 ``[E]``) and a CPU process group (``host_group``, e.g. gloo): the counts are then
-    gathered on the host and the device stream is never waited on.
+    synchronisation) and the permutations are computed on the device.  A caller that already holds
+    its counts on the host passes ``counts_host`` (CPU int64 ``[E]``) and a CPU process group
+    (``host_group``, e.g. gloo): counts are gathered and the whole plan is computed on the host, and
+    reaches the device as one copy from pinned memory, so the device stream is never waited on and
+    no small kernel is launched.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -62,26 +105,41 @@ def build_exchange_plan(
         flat_h = torch.empty(world * E, dtype=torch.int64)
         dist.all_gather_into_tensor(flat_h, counts_host.to(torch.int64).contiguous(), group=host_group)
         host_matrix = flat_h.view(world, E)
-        matrix = host_matrix.to(dev, non_blocking=True)
+        mine, cnt_es, shift_es, _ = _plan_from_matrix(host_matrix, rank, world)
+        total = int(mine.sum())
+        gather_h = torch.repeat_interleave(shift_es, cnt_es, output_size=total) + torch.arange(total)
+        scatter_h = torch.empty(total, dtype=torch.int64)
+        scatter_h[gather_h] = torch.arange(total)
+        lens_h = mine.sum(0)
+        parts = [gather_h, scatter_h, lens_h, flat_h]
+        numel = sum(p.numel() for p in parts)
+        if dev.type == "cuda":
+            staging = _pinned_pool.take(numel)
+            torch.cat(parts, out=staging[:numel])
+            packed = staging[:numel].to(dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(dev))
+            _pinned_pool.give_back(staging, ev)
+        else:
+            packed = torch.cat(parts)
+        gather_index, scatter_index, group_lens, mat = torch.split(packed, [p.numel() for p in parts])
+        matrix = mat.view(world, E)
     else:
         flat = torch.empty(world * E, dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(flat, counts_local.to(torch.int64).contiguous(), group=group)
         matrix = flat.view(world, E)
         host_matrix = matrix.cpu()  # the one host synchronisation of the exchange
+        mine, cnt_es, shift_es, _ = _plan_from_matrix(matrix, rank, world)
+        total = int(host_matrix[:, rank * e_loc : (rank + 1) * e_loc].sum())
+        ar = torch.arange(total, device=dev)
+        gather_index = torch.repeat_interleave(shift_es, cnt_es, output_size=total) + ar
+        scatter_index = torch.empty_like(gather_index)
+        scatter_index[gather_index] = ar
+        group_lens = mine.sum(0).contiguous()
     per_dest = host_matrix.view(world, world, e_loc).sum(-1)  # [src, dst]
     send_splits = per_dest[rank].tolist()
     recv_splits = per_dest[:, rank].tolist()
-    mine = matrix[:, rank * e_loc : (rank + 1) * e_loc]  # [src, e_local] rows arriving per source and expert
-    # arrival order is (source, expert); the grouped GEMM wants (expert, source)
-    arrive_start = (torch.cumsum(mine.reshape(-1), 0) - mine.reshape(-1)).view(world, e_loc)
-    cnt_es = mine.t().reshape(-1)  # segments in (expert, source) order
-    src_start_es = arrive_start.t().reshape(-1)
-    dst_start_es = torch.cumsum(cnt_es, 0) - cnt_es
-    total = int(sum(recv_splits))
-    gather_index = torch.repeat_interleave(src_start_es - dst_start_es, cnt_es, output_size=total) + torch.arange(
-        total, device=dev
-    )
-    return ExchangePlan(send_splits, recv_splits, gather_index, mine.sum(0).contiguous(), matrix)
+    return ExchangePlan(send_splits, recv_splits, gather_index, scatter_index, group_lens, matrix)
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -101,36 +159,20 @@ class _AllToAllRows(torch.autograd.Function):
         return gx, None, None, None
 
 
-class _GatherRows(torch.autograd.Function):
-    """y = x[index] for a permutation ``index``; backward scatters with the same permutation."""
+class _PermuteRows(torch.autograd.Function):
+    """y = x[index] for a permutation ``index`` with inverse ``inverse``.  Both directions are row
+    gathers (``index_select``): a gather streams at HBM speed, a scatter through ``index_copy_``
+    measured seven times slower on the same rows."""
 
     @staticmethod
-    def forward(ctx, x, index):
-        ctx.save_for_backward(index)
+    def forward(ctx, x, index, inverse):
+        ctx.save_for_backward(index, inverse)
         return x.index_select(0, index)
 
     @staticmethod
     def backward(ctx, g):
-        (index,) = ctx.saved_tensors
-        gx = torch.empty_like(g)
-        gx.index_copy_(0, index, g)
-        return gx, None
-
-
-class _ScatterRows(torch.autograd.Function):
-    """y[index] = x (inverse of _GatherRows)."""
-
-    @staticmethod
-    def forward(ctx, x, index):
-        ctx.save_for_backward(index)
-        y = torch.empty_like(x)
-        y.index_copy_(0, index, x)
-        return y
-
-    @staticmethod
-    def backward(ctx, g):
-        (index,) = ctx.saved_tensors
-        return g.index_select(0, index), None
+        index, inverse = ctx.saved_tensors
+        return g.index_select(0, inverse), None, None
 
 
 def expert_parallel_apply(
@@ -145,10 +187,169 @@ def expert_parallel_apply(
     if plan is None:
         plan = build_exchange_plan(counts_local, group)
     arrived = _AllToAllRows.apply(x_local, plan.send_splits, plan.recv_splits, group)
-    by_expert = _GatherRows.apply(arrived, plan.gather_index)
+    by_expert = _PermuteRows.apply(arrived, plan.gather_index, plan.scatter_index)
     y = local_fn(by_expert, plan.group_lens)
-    y_arrival_order = _ScatterRows.apply(y, plan.gather_index)
+    y_arrival_order = _PermuteRows.apply(y, plan.scatter_index, plan.gather_index)
     return _AllToAllRows.apply(y_arrival_order, plan.recv_splits, plan.send_splits, group)
+
+
+class BlockwiseLocalSteps:
+    """The device steps of one blockwise ``grouped_gemm_fp8`` forward + backward, callable one by one
+    (the same kernel calls ``FP8GroupedGemmBlockFunc`` makes) so that the expert-parallel wrapper can
+    place them around its exchanges.  A host-logic test substitutes plain-torch steps."""
+
+    def __init__(self, config, trans_b: bool, out_dtype: torch.dtype):
+        from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity
+
+        assert config.granularity == ScalingGranularity.BLOCKWISE and config.block_size == 128
+        self.config, self.trans_b, self.out_dtype = config, trans_b, out_dtype
+
+    def offsets(self, group_lens):
+        from primus_turbo_b200.pytorch.kernels.gemm_impl import group_offs_from_lens
+
+        return group_offs_from_lens(group_lens)
+
+    def _dt(self, fwd: bool):
+        from primus_turbo_b200.pytorch.ops.grouped_gemm_fp8 import _get_fp8_dtype
+
+        return _get_fp8_dtype(self.config.format, fwd)
+
+    def quant_weight(self, w):
+        from primus_turbo_b200.pytorch.kernels.quantization_impl import quant_fp8_blockwise_for_weight_impl
+
+        return quant_fp8_blockwise_for_weight_impl(w, self._dt(True), 128)
+
+    def quant_rows(self, x, lens, offs, fwd: bool):
+        """-> (row copy, column copy, row scales, column scales, padded lens, padded offsets)"""
+        from primus_turbo_b200.pytorch.kernels.quantization_impl import quant_fp8_blockwise_segment_m_row_col_impl
+
+        return quant_fp8_blockwise_segment_m_row_col_impl(x.contiguous(), self._dt(fwd), 128, lens, offs)
+
+    def _gemm(self, a, a_s, b8, b_s, lens, offs, trans_b):
+        from primus_turbo_b200.pytorch.kernels.gemm_impl import grouped_gemm_fp8_impl
+
+        return grouped_gemm_fp8_impl(
+            a, b8, a_s, b_s, lens, offs, trans_a=False, trans_b=trans_b, out_dtype=self.out_dtype,
+            granularity=self.config.granularity.value, num_cu=None,
+        )
+
+    def fwd(self, a_row, a_s_row, b8, b_s, lens, offs):
+        return self._gemm(a_row, a_s_row, b8, b_s, lens, offs, self.trans_b)
+
+    def dgrad(self, g_row, g_s_row, b8, b_s, lens, offs):
+        return self._gemm(g_row, g_s_row, b8, b_s, lens, offs, not self.trans_b)
+
+    def wgrad(self, a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs, num_cu=None):
+        from primus_turbo_b200.pytorch.kernels.gemm_impl import grouped_gemm_fp8_variable_k_impl
+
+        return grouped_gemm_fp8_variable_k_impl(
+            a_col, g_col, a_s_col, g_s_col, vk_lens, vk_offs, trans_a=True, trans_b=False, trans_c=self.trans_b,
+            out_dtype=self.out_dtype, granularity=self.config.granularity.value, num_cu=num_cu,
+        )
+
+
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=key)
+    return _side_streams[key]
+
+
+class _Fork:
+    """Runs a block of device work on a side stream that starts where the current stream stands
+    (``begin``) and is joined back later (``join``); on CPU tensors it does nothing."""
+
+    def __init__(self, ref: torch.Tensor):
+        self.cuda = ref.is_cuda
+        if self.cuda:
+            self.cur = torch.cuda.current_stream(ref.device)
+            self.side = _side_stream(ref.device)
+
+    def begin(self):
+        if self.cuda:
+            self.side.wait_stream(self.cur)
+
+    def stream(self):
+        import contextlib
+
+        return torch.cuda.stream(self.side) if self.cuda else contextlib.nullcontext()
+
+    def uses(self, *tensors):
+        """tensors allocated on the current stream that the side stream reads"""
+        if self.cuda:
+            for t in tensors:
+                t.record_stream(self.side)
+
+    def join(self, *produced):
+        """make the current stream wait for the side stream; `produced` were allocated there"""
+        if self.cuda:
+            self.cur.wait_stream(self.side)
+            for t in produced:
+                t.record_stream(self.cur)
+
+
+class _EPBlockwiseOverlapped(torch.autograd.Function):
+    """Dispatch -> blockwise grouped GEMM -> combine as one autograd node, so that the two steps that
+    need nothing from an exchange run beside it on a second stream: the weight quantisation beside
+    the forward dispatch, and wgrad beside the return of the activation gradient.  wgrad is a
+    persistent kernel (one CTA per SM): it is launched on ``148 - reserve_sms`` SMs so that the
+    collective's CTAs, launched first, and all of its own CTAs are resident together.
+
+    Measured on two B200s at the benchmark shape this form is *slower* than the serial chain
+    (12.9 ms against 11.8 ms per step): the weight quantisation, wgrad and the all-to-all are all
+    bound by HBM bandwidth, so running them side by side stretches each by what the other takes.
+    It stays selectable (``overlap=True``) for shapes whose local GEMMs are tensor-bound."""
+
+    @staticmethod
+    def forward(ctx, x_local, w_local, plan, group, steps, reserve_sms):
+        fork = _Fork(x_local)
+        fork.begin()
+        arrived = x_local.new_empty((sum(plan.recv_splits), *x_local.shape[1:]))
+        work = dist.all_to_all_single(
+            arrived, x_local.contiguous(), plan.recv_splits, plan.send_splits, group=group, async_op=True
+        )
+        with fork.stream():
+            b8, b_s = steps.quant_weight(w_local)
+        work.wait()
+        rows = arrived.index_select(0, plan.gather_index)
+        lens = plan.group_lens
+        offs = steps.offsets(lens)
+        a_row, a_col, a_s_row, a_s_col, _, _ = steps.quant_rows(rows, lens, offs, True)
+        fork.join(b8, b_s)
+        y = steps.fwd(a_row, a_s_row, b8, b_s, lens, offs)
+        y_arrival = y.index_select(0, plan.scatter_index)
+        out = y.new_empty((sum(plan.send_splits), *y.shape[1:]))
+        dist.all_to_all_single(out, y_arrival, plan.send_splits, plan.recv_splits, group=group)
+        ctx.save_for_backward(a_col, a_s_col, b8, b_s, lens, offs, plan.gather_index, plan.scatter_index)
+        ctx.plan, ctx.group, ctx.steps, ctx.reserve_sms = plan, group, steps, reserve_sms
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        a_col, a_s_col, b8, b_s, lens, offs, gather_index, scatter_index = ctx.saved_tensors
+        plan, group, steps = ctx.plan, ctx.group, ctx.steps
+        g_arrival = g.new_empty((sum(plan.recv_splits), *g.shape[1:]))
+        dist.all_to_all_single(g_arrival, g.contiguous(), plan.recv_splits, plan.send_splits, group=group)
+        gy = g_arrival.index_select(0, gather_index)
+        g_row, g_col, g_s_row, g_s_col, vk_lens, vk_offs = steps.quant_rows(gy, lens, offs, False)
+        ga = steps.dgrad(g_row, g_s_row, b8, b_s, lens, offs)
+        ga_arrival = ga.index_select(0, scatter_index)
+        gx = ga.new_empty((sum(plan.send_splits), *ga.shape[1:]))
+        fork = _Fork(g)
+        fork.begin()
+        work = dist.all_to_all_single(gx, ga_arrival, plan.send_splits, plan.recv_splits, group=group, async_op=True)
+        num_cu = None
+        if fork.cuda and ctx.reserve_sms > 0:
+            num_cu = max(1, torch.cuda.get_device_properties(g.device).multi_processor_count - ctx.reserve_sms)
+        with fork.stream():
+            fork.uses(a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs)
+            gw = steps.wgrad(a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs, num_cu)
+        work.wait()
+        fork.join(gw)
+        return gx, gw, None, None, None, None
 
 
 def ep_grouped_gemm_fp8(
@@ -159,9 +360,27 @@ def ep_grouped_gemm_fp8(
     trans_b: bool = True,
     config=None,
     plan: Optional[ExchangePlan] = None,
+    overlap: bool = False,
+    reserve_sms: int = 16,
+    steps=None,
 ) -> torch.Tensor:
-    """Expert-parallel ``grouped_gemm_fp8``: ``w_local`` holds this rank's ``E / world`` experts."""
+    """Expert-parallel ``grouped_gemm_fp8``: ``w_local`` holds this rank's ``E / world`` experts.
+
+    ``overlap=True`` (blockwise granularity only) uses the single-node form that runs the weight
+    quantisation beside the dispatch and wgrad beside the return of the activation gradient; the
+    results are bit-identical to ``overlap=False``.  ``steps`` replaces the device steps (tests).
+    """
     from primus_turbo_b200.pytorch.ops.grouped_gemm_fp8 import grouped_gemm_fp8
+
+    if overlap:
+        if plan is None:
+            plan = build_exchange_plan(counts_local, group)
+        if steps is None:
+            from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig
+
+            cfg = config if config is not None else Float8QuantConfig()
+            steps = BlockwiseLocalSteps(cfg, trans_b, torch.promote_types(x_local.dtype, w_local.dtype))
+        return _EPBlockwiseOverlapped.apply(x_local, w_local, plan, group, steps, reserve_sms)
 
     def local_fn(rows, group_lens):
         return grouped_gemm_fp8(rows, w_local, group_lens, trans_b=trans_b, config=config)

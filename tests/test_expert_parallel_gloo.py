@@ -95,3 +95,103 @@ def test_expert_parallel_exchange_world2(seed):
         (y_ref * coeff).sum().backward()
         assert torch.equal(results[r][0], y_ref.detach())
         assert torch.allclose(results[r][1], x.grad, rtol=0, atol=0)
+
+
+# ---- the overlapped single-node form (one autograd node around both exchanges) -------------------
+N_OUT = 4
+
+
+class _TorchSteps:
+    """Plain-torch stand-ins for the device steps: 'quantised' tensors are the tensors themselves."""
+
+    def offsets(self, lens):
+        return torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(lens, 0)])
+
+    def quant_weight(self, w):
+        return w, torch.ones(())
+
+    def quant_rows(self, x, lens, offs, fwd):
+        return x, x, None, None, lens, offs
+
+    @staticmethod
+    def _per_group(offs, fn):
+        o = offs.tolist()
+        return [fn(g, o[g], o[g + 1]) for g in range(len(o) - 1)]
+
+    def fwd(self, a_row, a_s_row, b8, b_s, lens, offs):
+        return torch.cat(self._per_group(offs, lambda g, lo, hi: a_row[lo:hi] @ b8[g].t()))
+
+    def dgrad(self, g_row, g_s_row, b8, b_s, lens, offs):
+        return torch.cat(self._per_group(offs, lambda g, lo, hi: g_row[lo:hi] @ b8[g]))
+
+    def wgrad(self, a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs, num_cu=None):
+        return torch.stack(self._per_group(vk_offs, lambda g, lo, hi: g_col[lo:hi].t() @ a_col[lo:hi]))
+
+
+def _weights(seed):
+    g = torch.Generator().manual_seed(100 + seed)
+    return torch.randn(E, N_OUT, H, generator=g, dtype=torch.float64)
+
+
+def _worker_overlapped(rank, store_path, seed, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    store = dist.FileStore(store_path, WORLD)
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=WORLD)
+    try:
+        from primus_turbo_b200.pytorch.dist.expert_parallel import ep_grouped_gemm_fp8
+
+        counts, xs = _routing(seed)
+        e_loc = E // WORLD
+        x = xs[rank].clone().requires_grad_(True)
+        w = _weights(seed)[rank * e_loc : (rank + 1) * e_loc].clone().requires_grad_(True)
+        y = ep_grouped_gemm_fp8(x, w, counts[rank], overlap=True, steps=_TorchSteps())
+        coeff = torch.arange(y.numel(), dtype=torch.float64).view_as(y) * 1e-2 + 1.0
+        (y * coeff).sum().backward()
+        out_q.put((rank, y.detach().tolist(), x.grad.tolist(), w.grad.tolist()))
+        dist.barrier()
+    except Exception as exc:
+        out_q.put((rank, repr(exc), None, None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_expert_parallel_overlapped_world2(seed):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_worker_overlapped, args=(r, path, seed, q)) for r in range(WORLD)]
+        for p in procs:
+            p.start()
+        results = {}
+        for _ in range(WORLD):
+            r, y, gx, gw = q.get(timeout=120)
+            assert gx is not None, f"rank {r} failed: {y}"
+            results[r] = (torch.tensor(y, dtype=torch.float64).reshape(-1, N_OUT),
+                          torch.tensor(gx, dtype=torch.float64).reshape(-1, H),
+                          torch.tensor(gw, dtype=torch.float64).reshape(-1, N_OUT, H))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    counts, xs = _routing(seed)
+    w_full = _weights(seed).clone().requires_grad_(True)
+    x_all, y_all = [], []
+    for r in range(WORLD):
+        x = xs[r].clone().requires_grad_(True)
+        outs, start = [], 0
+        for e in range(E):
+            n = int(counts[r, e])
+            outs.append(x[start : start + n] @ w_full[e].t())
+            start += n
+        y_ref = torch.cat(outs)
+        coeff = torch.arange(y_ref.numel(), dtype=torch.float64).view_as(y_ref) * 1e-2 + 1.0
+        x_all.append(x)
+        y_all.append((y_ref, coeff))
+    sum((y * c).sum() for y, c in y_all).backward()
+    e_loc = E // WORLD
+    for r in range(WORLD):
+        assert torch.allclose(results[r][0], y_all[r][0].detach(), rtol=0, atol=1e-12)
+        assert torch.allclose(results[r][1], x_all[r].grad, rtol=0, atol=1e-12)
+        assert torch.allclose(results[r][2], w_full.grad[r * e_loc : (r + 1) * e_loc], rtol=0, atol=1e-12)

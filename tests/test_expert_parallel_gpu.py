@@ -2,6 +2,8 @@
 same routed rows.  Forward output and activation gradient must be bit-identical (1x128 row scales
 and each output row do not depend on which other rows share a tile); weight gradients are compared
 within the GEMM gate because the 128-row column blocks are composed differently.
+Both forms are covered: the serial chain of autograd nodes and the single node that overlaps the
+weight quantisation and wgrad with the exchanges (same results bit for bit in out and grad_a).
 Skipped when fewer than two GPUs are visible."""
 
 import os
@@ -27,7 +29,7 @@ def _data():
     return counts, xs, gos, w
 
 
-def _worker(rank, store_path, q):
+def _worker(rank, store_path, q, overlap):
     torch.cuda.set_device(rank)
     store = dist.FileStore(store_path, WORLD)
     dist.init_process_group("nccl", store=store, rank=rank, world_size=WORLD, device_id=torch.device("cuda", rank))
@@ -40,7 +42,7 @@ def _worker(rank, store_path, q):
         e_loc = E // WORLD
         x = xs[rank].cuda().requires_grad_(True)
         w_loc = w[rank * e_loc : (rank + 1) * e_loc].cuda().requires_grad_(True)
-        out = ep_grouped_gemm_fp8(x, w_loc, counts[rank].cuda(), config=cfg)
+        out = ep_grouped_gemm_fp8(x, w_loc, counts[rank].cuda(), config=cfg, overlap=overlap)
         out.backward(gos[rank].cuda())
         torch.cuda.synchronize()
         q.put((rank, out.detach().float().cpu().tolist(), x.grad.float().cpu().tolist(), w_loc.grad.float().cpu().tolist()))
@@ -52,14 +54,15 @@ def _worker(rank, store_path, q):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_matches_single_gpu():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_expert_parallel_matches_single_gpu(overlap):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     with tempfile.TemporaryDirectory() as d:
-        procs = [ctx.Process(target=_worker, args=(r, os.path.join(d, "store"), q)) for r in range(WORLD)]
+        procs = [ctx.Process(target=_worker, args=(r, os.path.join(d, "store"), q, overlap)) for r in range(WORLD)]
         for p in procs:
             p.start()
         res = {}
