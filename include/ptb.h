@@ -198,9 +198,9 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
                                     ptb_stream_t stream);
 
 /* Every device-side wait in the GEMM kernels is bounded (2 s); a kernel whose wait runs out
- * records a non-zero code (1 copy producer, 2 MMA issuer, 3 epilogue) and leaves normally.
- * This call copies that code to *status (a host pointer) and optionally clears it.  It
- * synchronises with the device.  No counterpart in the reference. */
+ * records a non-zero code (1 copy producer, 2 MMA issuer, 3 epilogue, 4 scale loader) and
+ * leaves normally.  This call copies that code to *status (a host pointer) and optionally
+ * clears it.  It synchronises with the device.  No counterpart in the reference. */
 int ptb_gemm_status(int *status, int reset);
 
 #ifdef __cplusplus

@@ -83,10 +83,12 @@ template <typename T> struct Packed2;
 template <> struct Packed2<__nv_bfloat16> {
     using type = __nv_bfloat162;
     static __device__ __forceinline__ type zero() { return __floats2bfloat162_rn(0.f, 0.f); }
+    static __device__ __forceinline__ float2 to_float2(type v) { return __bfloat1622float2(v); }
 };
 template <> struct Packed2<__half> {
     using type = __half2;
     static __device__ __forceinline__ type zero() { return __floats2half2_rn(0.f, 0.f); }
+    static __device__ __forceinline__ float2 to_float2(type v) { return __half22float2(v); }
 };
 template <> struct Packed2<float> {
     using type = float2;
@@ -169,13 +171,15 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
     const int tid = threadIdx.x;
     const int tx  = tid & 15;  // 8-column fragment index inside the tile
     const int ty  = tid >> 4;  // row lane 0..15
-    const int64_t tiles_n = cdiv<int64_t>(p.N, kBlk);
-    const int64_t tiles_m = cdiv<int64_t>(SEGMENT ? (p.M + p.G * kBlk) : p.M, kBlk);
-    const int64_t tile    = blockIdx.x;
-    const int64_t tn      = tile % tiles_n;
-    const int64_t tmb     = tile / tiles_n;
-    const int64_t b       = SEGMENT ? 0 : tmb / tiles_m;
-    const int64_t tm      = SEGMENT ? tmb : tmb % tiles_m;
+    // the grid is at most 2^31 - 1 tiles (checked by the launcher): 32-bit divisions, a 64-bit one
+    // costs each thread ~80 instructions
+    const uint32_t tiles_n32 = (uint32_t) cdiv<int64_t>(p.N, kBlk);
+    const uint32_t tiles_m32 = (uint32_t) cdiv<int64_t>(SEGMENT ? (p.M + p.G * kBlk) : p.M, kBlk);
+    const uint32_t tmb32     = blockIdx.x / tiles_n32;
+    const int64_t tiles_n = tiles_n32, tiles_m = tiles_m32;
+    const int64_t tn      = blockIdx.x - tmb32 * tiles_n32;
+    const int64_t b       = SEGMENT ? 0 : tmb32 / tiles_m32;
+    const int64_t tm      = SEGMENT ? tmb32 : tmb32 - (uint32_t) b * tiles_m32;
 
     int64_t in_row0  = tm * kBlk; // first source row of this tile
     int64_t in_end   = p.M;       // first invalid source row
@@ -204,6 +208,49 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
     const int64_t col  = tn * kBlk + tx * 8;
     const bool vec_in  = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15u) == 0);
     const bool vec_out = (p.N % 8 == 0);
+
+    if constexpr (MODE == kMode2D && !SEGMENT && sizeof(T) == 2) {
+        // Interior 128x128 tile of a 16-bit weight: no per-row predicates, one running packed |x|
+        // maximum, packed fp32x2 scaling.  Same arithmetic as the general path below.
+        if (vec_in && in_row0 + kBlk <= p.M && (tn + 1) * kBlk <= p.N) {
+            using T2 = typename Packed2<T>::type;
+            const T *src = xb + (in_row0 + ty) * p.N + col;
+            uint4 raw[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4 *>(src + (int64_t) (16 * i) * p.N);
+            T2 m2 = Packed2<T>::zero();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const T2 *e = reinterpret_cast<const T2 *>(&raw[i]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) m2 = __hmax2(m2, __habs2(e[w]));
+            }
+            float m = warp_max(fmaxf(to_f32(m2.x), to_f32(m2.y)));
+            if ((tid & 31) == 0) s_red[tid >> 5] = m;
+            __syncthreads();
+            m = s_red[0];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+            float sc, sci;
+            scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+            const float2 sc2 = make_float2(sc, sc);
+            uint8_t *dst     = p.q_row + b * p.M * p.N + (in_row0 + ty) * p.N + col;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const T2 *e = reinterpret_cast<const T2 *>(&raw[i]);
+                uint32_t o[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float2 lo = __fmul2_rn(Packed2<T>::to_float2(e[2 * h]), sc2);
+                    const float2 hi = __fmul2_rn(Packed2<T>::to_float2(e[2 * h + 1]), sc2);
+                    o[h] = (uint32_t) cvt_fp8x2<FMT>(lo.x, lo.y) | ((uint32_t) cvt_fp8x2<FMT>(hi.x, hi.y) << 16);
+                }
+                *reinterpret_cast<uint2 *>(dst + (int64_t) (16 * i) * p.N) = make_uint2(o[0], o[1]);
+            }
+            if (tid == 0) p.s_2d[(b * tiles_m + tm) * tiles_n + tn] = sci;
+            return;
+        }
+    }
 
     RowFrag<T> frag[8];
     float rmax[8];
@@ -260,21 +307,32 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
         uint8_t *qb = p.q_row + b * p.M * p.N;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            float m = rmax[i];
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            float sc, sci;
-            scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+            for (int o = 8; o > 0; o >>= 1) rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], o));
+        }
+        // The two IEEE divisions per row are done once, by the lane whose index names the row, and the
+        // scale is handed to the other fifteen lanes by shuffle (sixteen redundant divisions per
+        // thread were a quarter of the kernel's instructions).
+        float mine = rmax[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) mine = ((tx & 7) == i) ? rmax[i] : mine;
+        float sc_mine, sci_mine;
+        scale_from_amax<FMT>(mine, kEpsBlock, sc_mine, sci_mine);
+        const int half_base = (tid & 31) & 16; // first lane of this thread's 16-lane row group
+        if (tx < 8) {
+            const int64_t r = in_row0 + ty + 16 * tx;
+            if (r < in_end) p.s_row[r * p.s_row_stride_m + tn * p.s_row_stride_nb] = sci_mine;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float sc  = __shfl_sync(0xffffffffu, sc_mine, half_base + i);
             const int64_t r = in_row0 + ty + 16 * i;
-            if (r < in_end) {
-                if (col < p.N) {
-                    float qv[8];
-                    frag[i].decode(qv);
+            if (r < in_end && col < p.N) {
+                float qv[8];
+                frag[i].decode(qv);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(qv[j], sc);
-                    store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
-                }
-                if (tx == 0) p.s_row[r * p.s_row_stride_m + tn * p.s_row_stride_nb] = sci;
+                for (int j = 0; j < 8; ++j) qv[j] = quant_val<FMT>(qv[j], sc);
+                store8_fp8<FMT>(qb + r * p.N, col, p.N, vec_out, qv);
             }
         }
     }
