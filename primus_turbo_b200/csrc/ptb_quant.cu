@@ -95,6 +95,19 @@ template <> struct Packed2<float> {
     static __device__ __forceinline__ type zero() { return make_float2(0.f, 0.f); }
 };
 
+template <int FMT, typename T> __device__ __forceinline__ void scale_store8_t(const uint4 &raw, const float2 (&s)[4], uint8_t *dst) {
+    using T2    = typename Packed2<T>::type;
+    const T2 *e = reinterpret_cast<const T2 *>(&raw);
+    uint32_t o[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float2 lo = __fmul2_rn(Packed2<T>::to_float2(e[2 * h]), s[2 * h]);
+        const float2 hi = __fmul2_rn(Packed2<T>::to_float2(e[2 * h + 1]), s[2 * h + 1]);
+        o[h] = (uint32_t) cvt_fp8x2<FMT>(lo.x, lo.y) | ((uint32_t) cvt_fp8x2<FMT>(hi.x, hi.y) << 16);
+    }
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
+}
+
 // One 8-element row fragment kept in its storage format: 16 bytes for 16-bit inputs, so a thread's
 // 8x8 share of the tile costs 32 registers and is decoded on the fly in each pass.
 template <typename T> struct RowFrag {
@@ -248,6 +261,82 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
                 *reinterpret_cast<uint2 *>(dst + (int64_t) (16 * i) * p.N) = make_uint2(o[0], o[1]);
             }
             if (tid == 0) p.s_2d[(b * tiles_m + tm) * tiles_n + tn] = sci;
+            return;
+        }
+    }
+
+    if constexpr (MODE != kMode2D && sizeof(T) == 2) {
+        // Interior tile (all 128 source rows and columns exist, 16-byte aligned rows) of a 16-bit
+        // input: the general path's per-row predicates and 64-bit index products are hoisted out.
+        // Same arithmetic, same results.
+        if (vec_in && in_row0 + kBlk <= in_end && (tn + 1) * kBlk <= p.N) {
+            using T2 = typename Packed2<T>::type;
+            const T *src       = xb + (in_row0 + ty) * p.N + col;
+            const int64_t step = 16 * p.N;
+            uint4 raw[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4 *>(src + i * step);
+            T2 cm2[4];
+            float rm[8];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) cm2[w] = Packed2<T>::zero();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const T2 *e = reinterpret_cast<const T2 *>(&raw[i]);
+                T2 a[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    a[w] = __habs2(e[w]);
+                    if constexpr (MODE & kModeCol) cm2[w] = __hmax2(cm2[w], a[w]);
+                }
+                const T2 m2 = __hmax2(__hmax2(a[0], a[1]), __hmax2(a[2], a[3]));
+                rm[i]       = fmaxf(to_f32(m2.x), to_f32(m2.y));
+            }
+            if constexpr (MODE & kModeRow) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) rm[i] = fmaxf(rm[i], __shfl_xor_sync(0xffffffffu, rm[i], o));
+                }
+                float mine = rm[0];
+#pragma unroll
+                for (int i = 1; i < 8; ++i) mine = ((tx & 7) == i) ? rm[i] : mine;
+                float sc_mine, sci_mine;
+                scale_from_amax<FMT>(mine, kEpsBlock, sc_mine, sci_mine);
+                if (tx < 8) p.s_row[(in_row0 + ty + 16 * tx) * p.s_row_stride_m + tn * p.s_row_stride_nb] = sci_mine;
+                const int half_base = (tid & 31) & 16;
+                uint8_t *dst        = p.q_row + b * p.M * p.N + (in_row0 + ty) * p.N + col;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float sc = __shfl_sync(0xffffffffu, sc_mine, half_base + i);
+                    const float2 s2[4] = {make_float2(sc, sc), make_float2(sc, sc), make_float2(sc, sc), make_float2(sc, sc)};
+                    scale_store8_t<FMT, T>(raw[i], s2, dst + i * step);
+                }
+            }
+            if constexpr (MODE & kModeCol) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    s_colmax[ty][tx * 8 + 2 * w]     = to_f32(cm2[w].x);
+                    s_colmax[ty][tx * 8 + 2 * w + 1] = to_f32(cm2[w].y);
+                }
+                __syncthreads();
+                if (tid < kBlk) {
+                    float m = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) m = fmaxf(m, s_colmax[k][tid]);
+                    float sc, sci;
+                    scale_from_amax<FMT>(m, kEpsBlock, sc, sci);
+                    s_colscale[tid]              = sc;
+                    p.s_col[tm * p.N + tn * kBlk + tid] = sci;
+                }
+                __syncthreads();
+                float2 s2[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) s2[w] = make_float2(s_colscale[tx * 8 + 2 * w], s_colscale[tx * 8 + 2 * w + 1]);
+                uint8_t *dst = p.q_col + (out_row0 + ty) * p.N + col;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) scale_store8_t<FMT, T>(raw[i], s2, dst + i * step);
+            }
             return;
         }
     }
