@@ -200,19 +200,20 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
 
     if constexpr (SEGMENT) {
         // find the group whose padded segment [var_k_offs[g], var_k_offs[g+1]) holds this tile
+        // (all four offsets of a candidate group are fetched in one round of independent loads, and a
+        // single barrier both publishes the hit and tells every thread whether there was one)
         const int64_t block_start = tm * kBlk;
-        if (tid == 0) s_seg[0] = 0;
-        __syncthreads();
+        int found                 = 0;
         for (int64_t g = tid; g < p.G; g += 256) {
             const int64_t ps = p.var_k_offs[g], pe = p.var_k_offs[g + 1];
+            const int64_t gs = p.group_offs[g], ge = p.group_offs[g + 1];
             if (block_start >= ps && block_start < pe) {
-                s_seg[0] = 1;
-                s_seg[1] = p.group_offs[g] + (block_start - ps);
-                s_seg[2] = p.group_offs[g + 1];
+                found    = 1;
+                s_seg[1] = gs + (block_start - ps);
+                s_seg[2] = ge;
             }
         }
-        __syncthreads();
-        if (s_seg[0] == 0) return; // tile lies beyond the last padded segment
+        if (!__syncthreads_or(found)) return; // tile lies beyond the last padded segment
         in_row0 = s_seg[1];
         in_end  = s_seg[2];
     }

@@ -59,3 +59,23 @@ def test_drop_in_alias():
     from primus_turbo.pytorch.ops import gemm_fp8, grouped_gemm_fp8, quantize_fp8  # noqa: F401
 
     assert C2 is Float8QuantConfig and turbo.float8_e4m3 is torch.float8_e4m3fn
+
+
+def test_float8_linear_conversion_mechanics():
+    """Construction and ``from_float`` (in place and copying) need no GPU; the forward does."""
+    from primus_turbo_b200.pytorch.modules import Float8Linear
+
+    lin = torch.nn.Linear(16, 8, bias=True)
+    w0, b0 = lin.weight.detach().clone(), lin.bias.detach().clone()
+    cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
+    copy = Float8Linear.from_float(lin, cfg, inplace=False)
+    assert type(lin) is torch.nn.Linear and isinstance(copy, Float8Linear) and copy.config is cfg
+    assert torch.equal(copy.weight, w0) and torch.equal(copy.bias, b0) and copy.weight is not lin.weight
+    same = Float8Linear.from_float(lin)
+    assert same is lin and isinstance(lin, Float8Linear)
+    assert lin.config.granularity == ScalingGranularity.TENSORWISE
+    assert "config=" in repr(lin)
+    nb = Float8Linear(4, 4, bias=False)
+    assert nb.bias is None and nb.config.granularity == ScalingGranularity.TENSORWISE
+    with pytest.raises(AssertionError):
+        Float8Linear.from_float(torch.nn.ReLU())
