@@ -155,6 +155,10 @@ __device__ __forceinline__ void cp_async_f32_zfill(float *dst_smem, const float 
                  "r"(valid ? 4u : 0u)
                  : "memory");
 }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // the barrier receives one arrival from this thread once all of its earlier cp.async copies have landed
 __device__ __forceinline__ void cp_async_arrive_on(uint32_t bar) {
@@ -307,6 +311,15 @@ struct Schedule {
 
 template <typename OutT> struct Pack8;
 template <> struct Pack8<__nv_bfloat16> {
+    static __device__ __forceinline__ uint4 pack(const float *v) {
+        uint4 o;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2bfloat162_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2bfloat162_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2bfloat162_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t *>(&t);
+        return o;
+    }
     static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float *v) {
         uint4 o;
         __nv_bfloat162 t;
@@ -318,6 +331,15 @@ template <> struct Pack8<__nv_bfloat16> {
     }
 };
 template <> struct Pack8<__half> {
+    static __device__ __forceinline__ uint4 pack(const float *v) {
+        uint4 o;
+        __half2 t;
+        t = __floats2half2_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2half2_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2half2_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t *>(&t);
+        t = __floats2half2_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t *>(&t);
+        return o;
+    }
     static __device__ __forceinline__ void store(__half *p, const float *v) {
         uint4 o;
         __half2 t;
@@ -329,6 +351,7 @@ template <> struct Pack8<__half> {
     }
 };
 template <> struct Pack8<float> {
+    static __device__ __forceinline__ uint4 pack(const float *) { return make_uint4(0, 0, 0, 0); } // 16-bit outputs only
     static __device__ __forceinline__ void store(float *p, const float *v) {
         *reinterpret_cast<float4 *>(p)     = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -576,6 +599,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                                ((args.c_group_stride * sizeof(OutT)) % 16 == 0);
         const bool tma_store  = (sizeof(OutT) == 2) && args.use_tma_store && !DEEP;
         uint8_t *my_stage     = c_stage + (warp - 4) * G_::kWarpCBytes;
+        const uint32_t stage_u32 = smem_u32(my_stage);
         bool store_pending    = false;
         float acc[kWgCols];
         while (ok && sched.get(t)) {
@@ -700,9 +724,10 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     }
 #pragma unroll
                     for (int j8 = 0; j8 < kWgCols / 8; ++j8) {
-                        OutT *dst = reinterpret_cast<OutT *>(my_stage + (j8 >> 3) * 4096 + lane * 128 +
-                                                             (((j8 & 7) ^ (lane & 7)) << 4));
-                        Pack8<OutT>::store(dst, &acc[j8 * 8]);
+                        // one 16-byte shared store per lane: a quarter-warp writes eight different
+                        // 16-byte columns of the swizzled slab (no bank conflict)
+                        const uint32_t dst = stage_u32 + (j8 >> 3) * 4096 + lane * 128 + (((j8 & 7) ^ (lane & 7)) << 4);
+                        st_shared_v4(dst, Pack8<OutT>::pack(&acc[j8 * 8]));
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
