@@ -203,6 +203,11 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
  * clears it.  It synchronises with the device.  No counterpart in the reference. */
 int ptb_gemm_status(int *status, int reset);
 
+/* Launches one warp that waits, with the same bounded wait, on a barrier nothing arrives on: after
+ * the limit (2 s) the kernel records status code 9 and returns normally.  It lets a host check the
+ * give-up path and its reporting without provoking a fault.  No counterpart in the reference. */
+int ptb_gemm_wait_selftest(ptb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,7 @@ _PROTOS = {
                              _I, _P],
     "ptb_grouped_gemm_fp8_variable_k": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _I, _P],
     "ptb_gemm_status": [ctypes.POINTER(c_int), _I],
+    "ptb_gemm_wait_selftest": [_P],
 }
 
 EXPORTS = ["ptb_version", "ptb_last_error", *_PROTOS.keys()]

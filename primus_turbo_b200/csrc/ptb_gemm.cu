@@ -771,6 +771,20 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
     }
 }
 
+// One warp waits on a barrier that nothing ever arrives on.  It exercises exactly the bounded wait the
+// GEMM roles use: the wait gives up after its limit, the kernel records a status code and returns
+// normally, and the context stays usable.
+__global__ void __launch_bounds__(32) wait_selftest_kernel() {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(smem_u32(&bar), 0);
+    if (!ok && threadIdx.x == 0) atomicExch(&g_gemm_status, 9);
+}
+
 // ---- host side -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -929,6 +943,12 @@ using namespace ptb;
 
 extern "C" {
 #pragma GCC visibility push(default)
+
+int ptb_gemm_wait_selftest(ptb_stream_t stream) {
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t) stream>>>();
+    PTB_LAUNCH_CHECK("wait_selftest_kernel");
+    return 0;
+}
 
 int ptb_gemm_status(int *status, int reset) {
     PTB_REQUIRE(status, PTB_ERR_ARG, "gemm_status: null pointer");

@@ -269,3 +269,30 @@ def test_llama_mlp_shape_tensorwise():
     ref = (xq[rows].float() @ wq.float().t()) * (x_s * w_s)
     assert O.rel_frobenius(ref.cpu(), out[rows].float().cpu()) <= FROB_TOL
     assert O.snr_db((x[rows].float() @ w.float().t()).cpu(), out[rows].float().cpu()) > SNR_E4M3_DB
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait that nothing satisfies returns after its 2 s limit: the kernel ends normally, the
+    status word holds the self-test's code, and the library keeps working afterwards."""
+    import time
+
+    import ctypes
+
+    from primus_turbo_b200 import _lib
+
+    assert _lib.gemm_status(reset=True) == 0
+    t0 = time.time()
+    _lib.check(_lib.lib.ptb_gemm_wait_selftest(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "selftest")
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.5 < waited < 10.0, waited
+    assert _lib.gemm_status(reset=True) == 9
+    assert _lib.gemm_status(reset=False) == 0
+    # the context is intact: a small GEMM still runs and is correct
+    a = torch.randn(128, 256, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(256, 256, device="cuda").to(torch.float8_e4m3fn)
+    one = torch.ones((), device="cuda")
+    out = gemm_fp8_impl(a, one, False, b, one, True, torch.float32, False, 1)
+    ref = a.float() @ b.float().t()
+    assert O.rel_frobenius(ref.cpu(), out.cpu()) < 1e-5
+    assert _lib.gemm_status(reset=True) == 0
