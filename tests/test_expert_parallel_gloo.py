@@ -1,4 +1,4 @@
-"""CPU, world_size 2 over gloo: the expert-parallel exchange (count all-gather, row all-to-all,
+"""CPU, world sizes 2 and 4 over gloo: the expert-parallel exchange (count all-gather, row all-to-all,
 expert-major permutation and the way back) against a single-process evaluation, forward and
 backward, including experts that receive no rows."""
 
@@ -10,12 +10,11 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-WORLD = 2
-E = 6  # 3 experts per rank
 H = 5
+SHAPES = [(2, 6), (4, 8)]  # (world size, experts): 3 and 2 experts per rank
 
 
-def _routing(seed):
+def _routing(seed, WORLD, E):
     g = torch.Generator().manual_seed(seed)
     counts = torch.randint(0, 7, (WORLD, E), generator=g)
     counts[:, 1] = 0  # an expert nobody routes to
@@ -28,14 +27,14 @@ def _expert_fn(e_global: int, rows: torch.Tensor) -> torch.Tensor:
     return rows * (e_global + 1.0) + rows.pow(2) * 0.5
 
 
-def _worker(rank, store_path, seed, out_q):
+def _worker(rank, store_path, seed, out_q, WORLD, E):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     store = dist.FileStore(store_path, WORLD)
     dist.init_process_group("gloo", store=store, rank=rank, world_size=WORLD)
     try:
         from primus_turbo_b200.pytorch.dist.expert_parallel import build_exchange_plan, expert_parallel_apply
 
-        counts, xs = _routing(seed)
+        counts, xs = _routing(seed, WORLD, E)
         x = xs[rank].clone().requires_grad_(True)
         e_loc = E // WORLD
 
@@ -65,13 +64,14 @@ def _worker(rank, store_path, seed, out_q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("WORLD,E", SHAPES)
 @pytest.mark.parametrize("seed", [0, 1])
-def test_expert_parallel_exchange_world2(seed):
+def test_expert_parallel_exchange(seed, WORLD, E):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "store")
-        procs = [ctx.Process(target=_worker, args=(r, path, seed, q)) for r in range(WORLD)]
+        procs = [ctx.Process(target=_worker, args=(r, path, seed, q, WORLD, E)) for r in range(WORLD)]
         for p in procs:
             p.start()
         results = {}
@@ -82,7 +82,7 @@ def test_expert_parallel_exchange_world2(seed):
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
-    counts, xs = _routing(seed)
+    counts, xs = _routing(seed, WORLD, E)
     for r in range(WORLD):
         x = xs[r].clone().requires_grad_(True)
         outs, start = [], 0
@@ -128,22 +128,22 @@ class _TorchSteps:
         return torch.stack(self._per_group(vk_offs, lambda g, lo, hi: g_col[lo:hi].t() @ a_col[lo:hi]))
 
 
-def _weights(seed):
+def _weights(seed, E):
     g = torch.Generator().manual_seed(100 + seed)
     return torch.randn(E, N_OUT, H, generator=g, dtype=torch.float64)
 
 
-def _worker_overlapped(rank, store_path, seed, out_q):
+def _worker_overlapped(rank, store_path, seed, out_q, WORLD, E):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     store = dist.FileStore(store_path, WORLD)
     dist.init_process_group("gloo", store=store, rank=rank, world_size=WORLD)
     try:
         from primus_turbo_b200.pytorch.dist.expert_parallel import ep_grouped_gemm_fp8
 
-        counts, xs = _routing(seed)
+        counts, xs = _routing(seed, WORLD, E)
         e_loc = E // WORLD
         x = xs[rank].clone().requires_grad_(True)
-        w = _weights(seed)[rank * e_loc : (rank + 1) * e_loc].clone().requires_grad_(True)
+        w = _weights(seed, E)[rank * e_loc : (rank + 1) * e_loc].clone().requires_grad_(True)
         y = ep_grouped_gemm_fp8(x, w, counts[rank], overlap=True, steps=_TorchSteps())
         coeff = torch.arange(y.numel(), dtype=torch.float64).view_as(y) * 1e-2 + 1.0
         (y * coeff).sum().backward()
@@ -156,13 +156,14 @@ def _worker_overlapped(rank, store_path, seed, out_q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("WORLD,E", SHAPES)
 @pytest.mark.parametrize("seed", [0, 1])
-def test_expert_parallel_overlapped_world2(seed):
+def test_expert_parallel_overlapped(seed, WORLD, E):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "store")
-        procs = [ctx.Process(target=_worker_overlapped, args=(r, path, seed, q)) for r in range(WORLD)]
+        procs = [ctx.Process(target=_worker_overlapped, args=(r, path, seed, q, WORLD, E)) for r in range(WORLD)]
         for p in procs:
             p.start()
         results = {}
@@ -175,8 +176,8 @@ def test_expert_parallel_overlapped_world2(seed):
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
-    counts, xs = _routing(seed)
-    w_full = _weights(seed).clone().requires_grad_(True)
+    counts, xs = _routing(seed, WORLD, E)
+    w_full = _weights(seed, E).clone().requires_grad_(True)
     x_all, y_all = [], []
     for r in range(WORLD):
         x = xs[r].clone().requires_grad_(True)

@@ -1,10 +1,10 @@
-"""GPU, 2 ranks over NCCL: expert-parallel ``grouped_gemm_fp8`` against the single-GPU op on the
+"""GPU, 2 / 4 / 8 ranks over NCCL (as many as are visible): expert-parallel ``grouped_gemm_fp8`` against the single-GPU op on the
 same routed rows.  Forward output and activation gradient must be bit-identical (1x128 row scales
 and each output row do not depend on which other rows share a tile); weight gradients are compared
 within the GEMM gate because the 128-row column blocks are composed differently.
 Both forms are covered: the serial chain of autograd nodes and the single node that overlaps the
 weight quantisation and wgrad with the exchanges (same results bit for bit in out and grad_a).
-Skipped when fewer than two GPUs are visible."""
+Cases that need more GPUs than are visible are skipped."""
 
 import os
 import tempfile
@@ -16,10 +16,10 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
-WORLD, E, K, N = 2, 8, 512, 384
+E, K, N = 8, 512, 384
 
 
-def _data():
+def _data(WORLD):
     g = torch.Generator().manual_seed(5)
     counts = torch.randint(0, 200, (WORLD, E), generator=g)
     counts[:, 3] = 0
@@ -29,7 +29,7 @@ def _data():
     return counts, xs, gos, w
 
 
-def _worker(rank, store_path, q, overlap):
+def _worker(rank, store_path, q, overlap, WORLD):
     torch.cuda.set_device(rank)
     store = dist.FileStore(store_path, WORLD)
     dist.init_process_group("nccl", store=store, rank=rank, world_size=WORLD, device_id=torch.device("cuda", rank))
@@ -38,7 +38,7 @@ def _worker(rank, store_path, q, overlap):
         from primus_turbo_b200.pytorch.dist.expert_parallel import ep_grouped_gemm_fp8
 
         cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
-        counts, xs, gos, w = _data()
+        counts, xs, gos, w = _data(WORLD)
         e_loc = E // WORLD
         x = xs[rank].cuda().requires_grad_(True)
         w_loc = w[rank * e_loc : (rank + 1) * e_loc].cuda().requires_grad_(True)
@@ -55,14 +55,15 @@ def _worker(rank, store_path, q, overlap):
 
 
 @pytest.mark.parametrize("overlap", [False, True])
-def test_expert_parallel_matches_single_gpu(overlap):
+@pytest.mark.parametrize("WORLD", [2, 4, 8])
+def test_expert_parallel_matches_single_gpu(overlap, WORLD):
     if torch.cuda.device_count() < WORLD:
-        pytest.skip("needs two GPUs")
+        pytest.skip(f"needs {WORLD} GPUs")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     with tempfile.TemporaryDirectory() as d:
-        procs = [ctx.Process(target=_worker, args=(r, os.path.join(d, "store"), q, overlap)) for r in range(WORLD)]
+        procs = [ctx.Process(target=_worker, args=(r, os.path.join(d, "store"), q, overlap, WORLD)) for r in range(WORLD)]
         for p in procs:
             p.start()
         res = {}
@@ -79,7 +80,7 @@ def test_expert_parallel_matches_single_gpu(overlap):
     from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
 
     cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
-    counts, xs, gos, w = _data()
+    counts, xs, gos, w = _data(WORLD)
     # single-GPU evaluation: rows of all ranks, expert-major with the source rank as minor order
     rows, grads, index = [], [], []
     for e in range(E):
