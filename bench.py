@@ -236,6 +236,31 @@ def _time_e2e(args, step, barrier, a, gy, rows_here, dev):
     return e2e_ms, h2d, d2h
 
 
+def _bind_host_threads_near_gpu(index: int) -> None:
+    """Pin this process to the CPU cores NVML reports as local to its GPU, so that the pinned host
+    buffers of the host-buffer pass are first-touched on that GPU's NUMA node (with several ranks
+    on one box the default placement funnels every rank's PCIe traffic through one node).  Only
+    reads device properties; any failure leaves the affinity as it was."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(index)
+        if hasattr(props, "pci_bus_id") and hasattr(props, "pci_domain_id"):  # robust to device remapping
+            bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        else:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        allowed = cpus & os.sched_getaffinity(0)
+        if len(allowed) >= 4:  # never squeeze the rank's host threads onto a couple of cores
+            os.sched_setaffinity(0, allowed)
+    except Exception:  # noqa: BLE001 - best effort, never fatal
+        pass
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -252,6 +277,8 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if world > 1 and args.bind_cpus:
+        _bind_host_threads_near_gpu(local_rank)
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
@@ -259,7 +286,16 @@ def run_ours(args):
             # the collective that runs beside wgrad must fit on the SMs wgrad leaves free
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.ep_reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
-        host_group = dist.new_group(backend="gloo")  # tiny CPU collective for the routing counts
+        host_group = dist.new_group(backend="gloo")  # CPU group: set-up traffic and the fallback count gather
+        if args.plan == "host":
+            # ranks of one machine exchange their routing counts through a shared-memory board
+            # (a gloo gather costs 2-4 ms per step at eight ranks and made the step host-bound)
+            try:
+                from primus_turbo_b200.pytorch.dist.expert_parallel import SharedCountsBoard
+
+                host_group = SharedCountsBoard(E_TOTAL, group=host_group)
+            except Exception as exc:  # noqa: BLE001 - keep the gloo group
+                print(f"[bench] shared counts board unavailable ({exc!r}); using gloo", file=sys.stderr)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     assert E_TOTAL % world == 0 and ROWS % world == 0
     cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
@@ -288,7 +324,10 @@ def run_ours(args):
         else:
             # the synthetic router's counts live on the host, so the exchange plan (rebuilt every
             # step, as routing changes every step in training) never waits on the device stream
-            plan = build_exchange_plan(counts_dev, counts_host=counts_here, host_group=host_group)
+            if args.plan == "host":
+                plan = build_exchange_plan(counts_dev, counts_host=counts_here, host_group=host_group)
+            else:
+                plan = build_exchange_plan(counts_dev)
             if args.ep_overlap:
                 # weight quantisation beside the dispatch, wgrad beside the return of grad_a
                 out = ep_grouped_gemm_fp8(a_in, w, counts_dev, config=cfg, plan=plan, overlap=True,
@@ -418,6 +457,11 @@ def main():
     ap.add_argument("--ep-overlap", type=int, default=0,
                     help="N > 1: 1 = weight quantise beside the dispatch and wgrad beside the grad_a return "
                          "(measured slower: both sides of each pair are HBM-bound); 0 = serial")
+    ap.add_argument("--plan", choices=["host", "device"], default="host",
+                    help="N > 1: where the exchange plan is computed (host: gloo gather + one pinned copy; "
+                         "device: NCCL gather + one host read of the split sizes)")
+    ap.add_argument("--bind-cpus", type=int, default=0,
+                    help="N > 1: 1 = pin each rank to the CPU cores NVML reports as local to its GPU")
     ap.add_argument("--ep-reserve-sms", type=int, default=16, help="SMs wgrad leaves to the overlapped collective")
     ap.add_argument("--experts", type=int, default=E_TOTAL, help="smaller case of the same workload (profiling)")
     ap.add_argument("--rows", type=int, default=ROWS, help="smaller case of the same workload (profiling)")

@@ -196,3 +196,58 @@ def test_expert_parallel_overlapped(seed, WORLD, E):
         assert torch.allclose(results[r][0], y_all[r][0].detach(), rtol=0, atol=1e-12)
         assert torch.allclose(results[r][1], x_all[r].grad, rtol=0, atol=1e-12)
         assert torch.allclose(results[r][2], w_full.grad[r * e_loc : (r + 1) * e_loc], rtol=0, atol=1e-12)
+
+
+# ---- shared-memory gather of the routing counts (ranks on one machine) ---------------------------
+def _worker_board(rank, store_path, out_q, WORLD, E):
+    import random
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    dist.init_process_group("gloo", store=dist.FileStore(store_path, WORLD), rank=rank, world_size=WORLD)
+    try:
+        from primus_turbo_b200.pytorch.dist.expert_parallel import SharedCountsBoard, build_exchange_plan
+
+        board = SharedCountsBoard(E)
+        rng = random.Random(rank)
+        ok = True
+        for call in range(40):
+            g = torch.Generator().manual_seed(1000 * call)  # every rank can rebuild the whole matrix
+            matrix = torch.randint(0, 50, (WORLD, E), generator=g)
+            if rng.random() < 0.3:
+                time.sleep(rng.random() * 0.003)  # ranks arrive at different times
+            got = board.all_gather_counts(matrix[rank])
+            ok = ok and torch.equal(got, matrix)
+        # the plan built through the board equals the one built through the gloo group
+        counts, _ = _routing(0, WORLD, E)
+        p_board = build_exchange_plan(counts[rank], counts_host=counts[rank], host_group=board)
+        p_gloo = build_exchange_plan(counts[rank], counts_host=counts[rank], host_group=dist.group.WORLD)
+        ok = ok and p_board.send_splits == p_gloo.send_splits and p_board.recv_splits == p_gloo.recv_splits
+        ok = ok and torch.equal(p_board.gather_index, p_gloo.gather_index)
+        ok = ok and torch.equal(p_board.scatter_index, p_gloo.scatter_index)
+        ok = ok and torch.equal(p_board.group_lens, p_gloo.group_lens)
+        ok = ok and torch.equal(p_board.counts_matrix, p_gloo.counts_matrix)
+        dist.barrier()
+        board.close()
+        out_q.put((rank, bool(ok)))
+    except Exception as exc:
+        out_q.put((rank, repr(exc)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("WORLD,E", [(4, 8)])
+def test_shared_counts_board(WORLD, E):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_worker_board, args=(r, os.path.join(d, "store"), q, WORLD, E)) for r in range(WORLD)]
+        for p in procs:
+            p.start()
+        for _ in range(WORLD):
+            r, ok = q.get(timeout=180)
+            assert ok is True, f"rank {r}: {ok}"
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
