@@ -13,6 +13,8 @@ Workload: 256 experts, hidden 7168, gate+up N=4096, 65536 routed rows, per-exper
 a multinomial over softmax(N(0,1) logits), seed 0; bf16 inputs, e4m3 payloads, fp32 scales.
 With N > 1 ranks the experts are sharded contiguously (256/N per GPU), the 65536 rows start evenly
 split over the ranks and travel to their expert's owner with an NCCL all-to-all (strong scaling).
+The per-step routing counts are gathered on the host through a shared-memory board (``--plan host``,
+default) or on the device (``--plan device``: NCCL gather plus one host read of the split sizes).
 
 Prints ONE JSON line on rank 0.  ``--impl reference`` times the CPU restatement of the reference's
 algorithm (oracle/, torch on the host cores) on a bounded sample of the same workload.
