@@ -52,6 +52,10 @@ class SharedCountsBoard:
     after every rank has written call ``s + 1``, which each does only after reading all of call
     ``s``, so a slot is never overwritten while someone still reads it.
 
+    The sequence number is stored after the counts and read before them; that is enough on hosts
+    with total store order (x86, which the HGX B200 boxes are).  A weakly ordered host CPU would need
+    a fence between the two stores.
+
     Construction is collective over ``group`` (any backend; one object broadcast).  ``close()`` (or
     process exit) drops the mapping; the creating rank removes the file.
     """
