@@ -2,9 +2,18 @@
  * ptb.h -- C ABI of the B200 (sm_100a) FP8 quantize / GEMM / grouped-GEMM library.
  *
  * Every entry point takes raw device pointers, explicit sizes/strides and a CUDA stream
- * (passed as void*, i.e. a cudaStream_t).  The library owns no memory: the caller allocates
- * every output and workspace.  All work is enqueued on the given stream; no call synchronises
- * the host with the device.  Calls are re-entrant and keep no state between calls.
+ * (passed as void*, i.e. a cudaStream_t).  The caller allocates every output and workspace.  All
+ * work is enqueued on the given stream; no call synchronises the host with the device (except
+ * ptb_gemm_status, which reads one word back).  Calls are re-entrant.  The library keeps no state
+ * between calls, with three stated exceptions: (1) ptb_quant_fp8_rowwise_noalloc reduces into one
+ * fixed device array that all of its calls share; (2) the GEMM kernels record a wait that ran out
+ * in one device word per GPU, shared by all streams and read with ptb_gemm_status; (3) per-device
+ * one-time set-up (kernel attributes, the address of that array) is cached in the process.
+ *
+ * Alignment: FP8 outputs of the blockwise quantise entry points (block1d, block1d_dual, block2d,
+ * segment_row_col) must be 8-byte aligned, GEMM operands 16-byte aligned with leading dimensions
+ * that are multiples of 16 bytes (PTB_ERR_ALIGN otherwise).  The tensorwise / rowwise quantise
+ * entry points accept any alignment and fall back to narrower accesses.
  *
  * Return value: 0 on success; a negative value for an argument error (PTB_ERR_*); a positive
  * value is a cudaError_t reported by the CUDA runtime or driver.  ptb_last_error() returns a
@@ -80,7 +89,8 @@ int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int6
  * training runtime that hands a plugin only its input and output buffers and owns every other byte
  * of the device, or a service that forbids cudaMalloc after start-up because the call stalls the
  * whole device.  Same arithmetic and outputs as ptb_quant_fp8_rowwise; the column-amax scratch is a
- * fixed 256 KiB array inside the library, so B*N may not exceed 65536 (PTB_ERR_TOO_LARGE otherwise).
+ * fixed 256 KiB array inside the library, so B*N may not exceed 65536 (PTB_ERR_TOO_LARGE otherwise;
+ * N == 1, the reduction over the innermost axis, uses no scratch and has no such limit).
  * The first call on each device looks the array's device address up (cudaGetSymbolAddress) and
  * should therefore be made before any stream capture starts.  All calls share the one array, which
  * keeps whatever the previous call left in it (each call clears the part it uses): two calls that

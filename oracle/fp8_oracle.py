@@ -318,6 +318,26 @@ def grouped_gemm_rowwise(aq, a_s, bq, b_s, group_offs, trans_b=True, out_dtype=t
     return out.to(out_dtype)
 
 
+def grouped_gemm_variable_k_scaled(lhs_q, lhs_s, rhs_q, rhs_s, group_offs, out_dtype=torch.bfloat16):
+    """Variable-K grouped GEMM with one scale per output row / column (rowwise) or one scalar each
+    (tensorwise): C[g] = (lhs[offs[g]:offs[g+1]]^T . rhs[offs[g]:offs[g+1]]) * ls[:, None] * rs[None, :].
+    The group boundaries are the unpadded row offsets, so a group's contraction range need not be a
+    multiple of 128 (primus_turbo/pytorch/ops/grouped_gemm_fp8.py:345-393 rowwise wgrad, :522-568
+    tensorwise wgrad; kernel semantics primus_turbo/triton/grouped_gemm/grouped_gemm_fp8_kernel.py,
+    masked K loop).  Empty group -> zeros.  Output [G, OUT_M, OUT_N]."""
+    G = group_offs.numel() - 1
+    OUT_M, OUT_N = lhs_q.shape[1], rhs_q.shape[1]
+    ls = lhs_s.to(torch.float32).reshape(-1, 1) if lhs_s.numel() > 1 else lhs_s.to(torch.float32).reshape(1, 1)
+    rs = rhs_s.to(torch.float32).reshape(1, -1) if rhs_s.numel() > 1 else rhs_s.to(torch.float32).reshape(1, 1)
+    out = torch.zeros((G, OUT_M, OUT_N), dtype=torch.float32)
+    for g in range(G):
+        lo, hi = int(group_offs[g]), int(group_offs[g + 1])
+        if hi > lo:
+            acc = lhs_q[lo:hi].to(torch.float32).t() @ rhs_q[lo:hi].to(torch.float32)
+            out[g] = acc * (ls * rs)
+    return out.to(out_dtype)
+
+
 # ----------------------------------------------------------------------------------------------
 # comparators (tests/pytorch/test_utils.py:37-74)
 # ----------------------------------------------------------------------------------------------

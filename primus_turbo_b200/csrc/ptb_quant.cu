@@ -4,6 +4,8 @@
 // (twice for the two-pass tensorwise / rowwise reductions, whose second pass is served largely
 // from the 126 MB L2), keeps the tile in registers, reduces the amax with warp shuffles and
 // shared memory, and writes FP8 with 8-byte stores.
+#include <atomic>
+
 #include "ptb_common.cuh"
 
 namespace ptb {
@@ -497,6 +499,9 @@ int launch_block_quant(const BlockQuantArgs &a, int x_dtype, int q_dtype, cudaSt
     const int64_t tiles_n = cdiv<int64_t>(a.N, kBlk);
     if (tiles_m == 0 || tiles_n == 0) return 0;
     PTB_REQUIRE(tiles_n * tiles_m <= 2147483647LL, PTB_ERR_TOO_LARGE, "tile grid too large");
+    // every path of the tile kernel writes FP8 with 8-byte stores
+    PTB_REQUIRE((reinterpret_cast<uintptr_t>(a.q_row) & 7u) == 0 && (reinterpret_cast<uintptr_t>(a.q_col) & 7u) == 0,
+                PTB_ERR_ALIGN, "blockwise quantise: FP8 output pointers must be 8-byte aligned");
     const unsigned grid = (unsigned) (tiles_m * tiles_n);
     PTB_SWITCH_HP(x_dtype, T, PTB_SWITCH_FP8(q_dtype, FMT,
         (quant_block_kernel<T, FMT, MODE, SEGMENT><<<grid, 256, 0, st>>>(a))));
@@ -829,29 +834,37 @@ int ptb_quant_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int6
 static __device__ __align__(256) float g_noalloc_rowwise_scratch[PTB_NOALLOC_MAX_COLUMNS];
 
 // Device address of the array above on the current device.  The array's name is only a host-side
-// handle here, so the address is asked for once per device and remembered.
+// handle here, so the address is asked for once per device and remembered.  The cache entries are
+// atomics: two host threads that make a device's first call together both look the address up and
+// store the same value.  A cudaDeviceReset invalidates the cache; a process that resets a device
+// must not call this entry point on it afterwards.
 static int noalloc_scratch_address(float **out) {
-    static float *address_on_device[64] = {};
+    static std::atomic<float *> address_on_device[64];
     int dev = -1;
     PTB_CUDA(cudaGetDevice(&dev));
     PTB_REQUIRE(dev >= 0 && dev < 64, PTB_ERR_UNSUPPORTED, "quant_rowwise_noalloc: device index %d not supported", dev);
-    if (address_on_device[dev] == nullptr) {
-        float *p = nullptr;
+    float *p = address_on_device[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         PTB_CUDA(cudaGetSymbolAddress((void **) &p, g_noalloc_rowwise_scratch));
         PTB_REQUIRE(p != nullptr, PTB_ERR_DRIVER, "quant_rowwise_noalloc: scratch array has no device address");
-        address_on_device[dev] = p;
+        address_on_device[dev].store(p, std::memory_order_release);
     }
-    *out = address_on_device[dev];
+    *out = p;
     return 0;
 }
 
 int ptb_quant_fp8_rowwise_noalloc(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, void *q, int q_dtype,
                                   float *scale_inv, ptb_stream_t stream) {
     PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "quant_rowwise_noalloc: negative size");
-    PTB_REQUIRE(B * N <= (int64_t) PTB_NOALLOC_MAX_COLUMNS, PTB_ERR_TOO_LARGE,
-                "quant_rowwise_noalloc: B*N = %lld scale columns exceed the built-in scratch of %d; use "
-                "ptb_quant_fp8_rowwise with a caller-provided workspace",
-                (long long) (B * N), PTB_NOALLOC_MAX_COLUMNS);
+    // N == 1 (the reduction axis is the innermost one) reduces inside one CTA and uses no scratch
+    if (N == 1) return ptb_quant_fp8_rowwise(x, x_dtype, B, M, N, q, q_dtype, scale_inv, nullptr, stream);
+    // bound each factor before multiplying: the product of two huge sizes could wrap
+    PTB_REQUIRE(B <= (int64_t) PTB_NOALLOC_MAX_COLUMNS && N <= (int64_t) PTB_NOALLOC_MAX_COLUMNS &&
+                    B * N <= (int64_t) PTB_NOALLOC_MAX_COLUMNS,
+                PTB_ERR_TOO_LARGE,
+                "quant_rowwise_noalloc: B = %lld times N = %lld scale columns exceed the built-in scratch of %d; "
+                "use ptb_quant_fp8_rowwise with a caller-provided workspace",
+                (long long) B, (long long) N, PTB_NOALLOC_MAX_COLUMNS);
     float *scratch = nullptr;
     int rc = noalloc_scratch_address(&scratch);
     if (rc) return rc;

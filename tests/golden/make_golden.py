@@ -16,6 +16,16 @@ Two families of fixtures are written:
   16-bit tensorwise inputs the reference's torch code multiplies in 16-bit precision (a 0-dim
   fp32 scale does not promote), which its own tests absorb with tolerances; those cases are stored
   with ``exact = 0`` and compared the way the reference compares them.
+* ``ref_blockwise_interp.npz`` -- outputs of the REFERENCE's own Triton blockwise quantise kernels
+  (primus_turbo/triton/quantization/quant_blockwise.py, imported unmodified and executed on CPU
+  tensors by Triton's interpreter, ``TRITON_INTERPRET=1``): 1-D blocks along both axes, the dual
+  kernel, the 128x128 weight kernel and the grouped ``segment_m_row_col`` kernel, on shapes with
+  partial tiles, empty and one-row groups.  Outputs are pre-filled with sentinels so that positions the
+  reference never writes are recorded too.  These pin the layouts (padded segment rows, the
+  ``[ceil(N/128), M]`` order of the row scales, padded offsets), every scale bit for bit, and the FP8
+  bytes wherever the interpreter's float-to-e4m3 cast is sound: that cast (numpy emulation, not the
+  GPU instruction) rounds ties away from zero, mis-rounds values that round up into the next binade
+  and truncates subnormals, so the tests skip exactly those positions and demand equality elsewhere.
 * ``oracle_c1.npz`` -- the CPU oracle on the small benchmark configuration (A bf16 [256,1024]
   ~N(0,1), B bf16 [512,1024] ~N(0,0.02), seed 0): scales in full, FP8 payloads as SHA-256 digests
   plus their leading bytes, bf16 output digest.  It freezes the oracle and lets the GPU tests check
@@ -71,6 +81,71 @@ def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(_bits(t).tobytes()).hexdigest()
 
 
+SENT_Q = 0x55  # byte pre-filled into FP8 outputs (positions the reference leaves unwritten keep it)
+SENT_S = -777.0  # value pre-filled into scale outputs
+
+
+def write_blockwise_interp(ref_root: Path) -> None:
+    """Run the reference's Triton blockwise quantise kernels on CPU tensors through the interpreter.
+    Must run in a process started with TRITON_INTERPRET=1 (main() re-executes itself for this)."""
+    import os
+    import subprocess
+
+    if os.environ.get("TRITON_INTERPRET") != "1":
+        env = dict(os.environ, TRITON_INTERPRET="1")
+        subprocess.run([sys.executable, __file__, str(ref_root), "--blockwise-only"], check=True, env=env)
+        return
+    spec = importlib.util.spec_from_file_location(
+        "ref_quant_blockwise", ref_root / "primus_turbo" / "triton" / "quantization" / "quant_blockwise.py")
+    qb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(qb)
+    gen = torch.Generator().manual_seed(77)
+    out = {}
+
+    def q_buf(*shape):
+        return torch.full(shape, SENT_Q, dtype=torch.uint8).view(E4)
+
+    def s_buf(*shape):
+        return torch.full(shape, SENT_S, dtype=torch.float32)
+
+    cd = lambda a, b: (a + b - 1) // b  # noqa: E731
+    # 1-D blocks, both axes, and the dual kernel: partial tiles in both dimensions
+    M, N = 200, 192
+    x = torch.randn(M, N, generator=gen).to(torch.bfloat16)
+    x[5, :128] *= 1e-6  # a block below the 1e-4 amax floor
+    out["b1_x"] = _bits(x)
+    for axis in (1, 0):
+        q, s = q_buf(M, N), s_buf(*((M, cd(N, 128)) if axis == 1 else (cd(M, 128), N)))
+        qb.quant_fp8_blockwise_kernel[(cd(M, 128), cd(N, 128))](x, q, s, M, N, BLOCK_SIZE=128, FP8_MAX=448.0, AXIS=axis)
+        out[f"b1_q_axis{axis}"], out[f"b1_s_axis{axis}"] = _bits(q), _bits(s)
+    qr, sr, qc, sc = q_buf(M, N), s_buf(M, cd(N, 128)), q_buf(M, N), s_buf(cd(M, 128), N)
+    qb.quant_fp8_blockwise_dual_kernel[(cd(M, 128), cd(N, 128))](x, qr, sr, qc, sc, M, N, BLOCK_SIZE=128, FP8_MAX=448.0)
+    out["dual_q_row"], out["dual_s_row"], out["dual_q_col"], out["dual_s_col"] = _bits(qr), _bits(sr), _bits(qc), _bits(sc)
+    # 128x128 weight blocks, batched
+    B, Mw, Nw = 2, 136, 192
+    w = (torch.randn(B, Mw, Nw, generator=gen) * 0.02).to(torch.bfloat16)
+    q, s = q_buf(B, Mw, Nw), s_buf(B, cd(Mw, 128), cd(Nw, 128))
+    qb.quant_fp8_blockwise_for_weight_kernel[(B, cd(Mw, 128), cd(Nw, 128))](w, q, s, Mw, Nw, BLOCK_SIZE=128, FP8_MAX=448.0)
+    out["w_x"], out["w_q"], out["w_s"] = _bits(w), _bits(q), _bits(s)
+    # grouped segment row + column: empty group, one-row group, lengths around 128, rows past the last group
+    lens = torch.tensor([100, 0, 257, 1, 129], dtype=torch.int64)
+    offs = O.group_offs_from_lens(lens)
+    G, Ms, Ns = lens.numel(), int(offs[-1]) + 6, 192
+    xs = torch.randn(Ms, Ns, generator=gen).to(torch.bfloat16)
+    vk_lens = ((lens + 127) // 128) * 128  # primus_turbo/pytorch/kernels/quantization/quantization_impl.py:428-430
+    vk_offs = torch.zeros(G + 1, dtype=torch.int64)
+    vk_offs[1:] = torch.cumsum(vk_lens, 0)
+    m_pad = Ms + G * 128
+    qr, qc = q_buf(Ms, Ns), q_buf(m_pad, Ns)
+    sr, sc = s_buf(cd(Ns, 128), Ms), s_buf(cd(m_pad, 128), Ns)
+    qb.quant_fp8_blockwise_segment_m_row_col_kernel[(cd(m_pad, 128), cd(Ns, 128))](
+        xs, qr, qc, sr, sc, offs, vk_offs, Ms, Ns, G, BLOCK_SIZE=128, FP8_MAX=448.0)
+    out["seg_x"], out["seg_lens"] = _bits(xs), lens.numpy()
+    out["seg_q_row"], out["seg_q_col"], out["seg_s_row"], out["seg_s_col"] = _bits(qr), _bits(qc), _bits(sr), _bits(sc)
+    out["seg_vk_offs"] = vk_offs.numpy()
+    np.savez_compressed(HERE / "ref_blockwise_interp.npz", **out)
+
+
 def main(ref_root: str) -> None:
     mods, lp = _load_reference_refs(Path(ref_root))
     qref = mods["quantization_ref"]
@@ -116,6 +191,9 @@ def main(ref_root: str) -> None:
     out = gref.grouped_gemm_ref(a, b, lens, trans_b=True)
     np.savez_compressed(HERE / "ref_grouped_gemm.npz", a=_bits(a), b=_bits(b), lens=lens.numpy(), out=_bits(out))
 
+    # ---- reference Triton blockwise kernels under the interpreter --------------------------------
+    write_blockwise_interp(Path(ref_root))
+
     # ---- oracle on the small benchmark configuration ------------------------------------------------
     g0 = torch.Generator().manual_seed(0)
     A = torch.randn(256, 1024, generator=g0).to(torch.bfloat16)
@@ -134,6 +212,9 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) == 3 and sys.argv[2] == "--blockwise-only":
+        write_blockwise_interp(Path(sys.argv[1]))
+    elif len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
-    main(sys.argv[1])
+    else:
+        main(sys.argv[1])

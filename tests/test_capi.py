@@ -54,6 +54,12 @@ def test_argument_errors_are_reported_without_a_device():
     assert rc == -5 and b"groups" in L.ptb_last_error()
     with pytest.raises(_lib.PtbError):
         _lib.check(rc, "ptb_grouped_gemm_fp8")
+    # a misaligned FP8 output of a blockwise quantise is an error code, never a device fault
+    # (the pointers are only inspected on the host; nothing is launched)
+    rc = L.ptb_quant_fp8_block1d(0x1000, _lib.PTB_BF16, 128, 128, 1, 0x2004, _lib.PTB_E4M3, 0x3000, None)
+    assert rc == -3 and b"8-byte" in L.ptb_last_error()
+    rc = L.ptb_quant_fp8_block2d(0x1000, _lib.PTB_BF16, 1, 128, 128, 0x2001, _lib.PTB_E4M3, 0x3000, None)
+    assert rc == -3
     # empty problems succeed trivially
     assert L.ptb_quant_fp8_block2d(None, 2, 0, 128, 128, None, 3, None, None) == 0
     assert L.ptb_transpose_2d_u8(None, 1, 0, 8, None, None) == 0

@@ -184,3 +184,42 @@ def test_quantize_traces_as_one_graph():
     assert_quant_equal(q, s, qo, so)
     q, s = fn(x, E4, G.TENSORWISE)
     assert_quant_equal(q, s, *O.quant_tensorwise(x.cpu(), E4))
+
+
+def test_blockwise_kernels_match_reference_triton_fixture():
+    """The CUDA blockwise quantisers against outputs of the reference's own Triton kernels (captured on
+    CPU by Triton's interpreter, tests/golden/make_golden.py): scale bits, layouts, and FP8 bytes
+    wherever the interpreter's cast is sound (tests/golden_util.py)."""
+    from tests import golden_util as GU
+
+    z = GU.load()
+    x = GU.bf16(z["b1_x"])
+    xd = x.to(DEV)
+    for axis, mode in ((1, "row"), (0, "col")):
+        q, s = quantize_fp8(xd, E4, G.BLOCKWISE, block_size=128, axis=axis)
+        GU.assert_scales_equal(s, GU.f32(z[f"b1_s_axis{axis}"]), f"1-D axis {axis}")
+        GU.assert_payload_matches(q, GU.u8(z[f"b1_q_axis{axis}"]), x, GU.forward_scale(x, mode), f"1-D axis {axis}")
+    q_row, s_row, q_col, s_col = quantize_fp8_with_trans(xd, E4, G.BLOCKWISE, block_size=128)
+    GU.assert_scales_equal(s_row, GU.f32(z["dual_s_row"]), "dual row")
+    GU.assert_scales_equal(s_col, GU.f32(z["dual_s_col"]), "dual col")
+    GU.assert_payload_matches(q_row, GU.u8(z["dual_q_row"]), x, GU.forward_scale(x, "row"), "dual row")
+    GU.assert_payload_matches(q_col, GU.u8(z["dual_q_col"]), x, GU.forward_scale(x, "col"), "dual col")
+    w = GU.bf16(z["w_x"])
+    q, s = quantize_fp8(w.to(DEV), E4, G.BLOCKWISE, block_size=128, scaling_recipe=ScalingRecipe(use_2d_block=True))
+    GU.assert_scales_equal(s, GU.f32(z["w_s"]), "128x128 weight")
+    GU.assert_payload_matches(q, GU.u8(z["w_q"]), w, GU.forward_scale(w, "2d"), "128x128 weight")
+    xs = GU.bf16(z["seg_x"])
+    lens = torch.from_numpy(z["seg_lens"])
+    ref_vk = torch.from_numpy(z["seg_vk_offs"])
+    offs_dev = group_offs_from_lens(lens.to(DEV))
+    q_row, q_col, s_row, s_col, vk_lens, vk_offs = quant_fp8_blockwise_segment_m_row_col_impl(
+        xs.to(DEV), E4, 128, lens.to(DEV), offs_dev)
+    assert torch.equal(vk_offs.cpu(), ref_vk)
+    mu, pu = int(lens.sum()), int(ref_vk[-1])
+    GU.assert_scales_equal(s_row[:, :mu].contiguous(), GU.f32(z["seg_s_row"])[:, :mu].contiguous(), "segment row scales")
+    GU.assert_payload_matches(q_row[:mu], GU.u8(z["seg_q_row"])[:mu], xs[:mu], GU.forward_scale(xs[:mu], "row"),
+                              "segment row copy")
+    xp = GU.padded_segments(xs, lens, ref_vk)
+    GU.assert_scales_equal(s_col[: pu // 128], GU.f32(z["seg_s_col"])[: pu // 128].contiguous(), "segment column scales")
+    GU.assert_payload_matches(q_col[:pu], GU.u8(z["seg_q_col"])[:pu], xp, GU.forward_scale(xp, "col"),
+                              "segment column copy")

@@ -8,10 +8,10 @@ exactly what the workspace variant produces -- FP8 bytes and scale bits -- on ba
 it must refuse shapes that do not fit the array.
 """
 
-import ctypes
-
 import pytest
 import torch
+
+from oracle import fp8_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -45,11 +45,21 @@ def test_noalloc_matches_workspace_variant_twice_in_a_row():
         q, s = _run("ptb_quant_fp8_rowwise_noalloc", x, with_workspace=False)
         assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
         assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+        # and the entry point stands on its own against the CPU oracle of the reference arithmetic
+        q_cpu, s_cpu = O.quant_rowwise(x.cpu(), E4, 1)
+        assert O.bits_equal_f32(s.cpu(), s_cpu) and O.bytes_equal(q.cpu(), q_cpu)
     # innermost-axis case (N == 1) goes through the same entry point and needs no scratch at all
     rows = torch.randn(300, 515, 1, device="cuda", dtype=torch.float16)
     q_ref, s_ref = _run("ptb_quant_fp8_rowwise", rows, with_workspace=True)
     q, s = _run("ptb_quant_fp8_rowwise_noalloc", rows, with_workspace=False)
     assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32)) and torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    q_cpu, s_cpu = O.quant_rowwise(rows.cpu(), E4, 1)
+    assert O.bits_equal_f32(s.cpu(), s_cpu) and O.bytes_equal(q.cpu(), q_cpu)
+    # that case has no size limit: more rows than the scratch has words
+    many = torch.randn(70000, 64, 1, device="cuda", dtype=torch.bfloat16)
+    q, s = _run("ptb_quant_fp8_rowwise_noalloc", many, with_workspace=False)
+    q_cpu, s_cpu = O.quant_rowwise(many.cpu(), E4, 1)
+    assert O.bits_equal_f32(s.cpu(), s_cpu) and O.bytes_equal(q.cpu(), q_cpu)
 
 
 def test_noalloc_rejects_shapes_beyond_its_scratch():
@@ -61,3 +71,6 @@ def test_noalloc_rejects_shapes_beyond_its_scratch():
         torch.cuda.current_stream().cuda_stream,
     )
     assert rc == -5 and b"65536" in _lib.lib.ptb_last_error()
+    # sizes whose product wraps a 64-bit integer are refused as well (no pointer is touched)
+    rc = _lib.lib.ptb_quant_fp8_rowwise_noalloc(None, _lib.PTB_BF16, 1 << 32, 2, 1 << 32, None, _lib.PTB_E4M3, None, None)
+    assert rc == -5
