@@ -181,6 +181,8 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
  *   a [M_total, K]; b [G, N, K] (trans_b = 1) or [G, K, N] (trans_b = 0), contiguous;
  *   group_offs: device int64 [G+1].  Scales as in ptb_gemm_fp8 with an extra group stride on b
  *   (blockwise: a_scale is indexed by absolute row; b_scale by (g, n/128, kb)).
+ * At most 1024 groups per call (the kernel keeps its tile table in shared memory;
+ * PTB_ERR_TOO_LARGE beyond that -- split the call).
  * Replaces primus_turbo::grouped_gemm_fp8_impl
  * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:817-859) including its
  * tail-zeroing launch. */
@@ -199,6 +201,8 @@ int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b,
  *                   [rows/128, OUT_M] and [rows/128, OUT_N], applied per 128-row block.
  *   PTB_ROWWISE:    lhs_scale[OUT_M], rhs_scale[OUT_N] applied to the finished tile; any offsets.
  *   PTB_TENSORWISE: lhs_scale[1], rhs_scale[1]; any offsets.
+ * With unpadded offsets the rows of lhs / rhs outside a group's range never reach its result,
+ * whatever bytes they hold.  At most 1024 groups per call.
  * Replaces primus_turbo::grouped_gemm_fp8_variable_k_impl (grouped_gemm_fp8_impl.py:862-901). */
 int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_lhs,
                                     const void *rhs, int rhs_dtype, int64_t ld_rhs, void *out,
@@ -210,7 +214,9 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
 /* Every device-side wait in the GEMM kernels is bounded (2 s); a kernel whose wait runs out
  * records a non-zero code (1 copy producer, 2 MMA issuer, 3 epilogue, 4 scale loader) and
  * leaves normally.  This call copies that code to *status (a host pointer) and optionally
- * clears it.  It synchronises with the device.  No counterpart in the reference. */
+ * clears it.  It synchronises with the device.  The code is one word per GPU, shared by every
+ * stream and caller of the library in the process: a non-zero value says that some GEMM launched
+ * since the last reset gave up, not which one.  No counterpart in the reference. */
 int ptb_gemm_status(int *status, int reset);
 
 /* Launches one warp that waits, with the same bounded wait, on a barrier nothing arrives on: after

@@ -94,6 +94,10 @@ def check(rc: int, what: str) -> None:
 KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_rowwise_noalloc": 2,
                     "ptb_quant_fp8_segment_row_col": 2,
                     "ptb_gemm_status": 0}
+# PTB_DEBUG_STATUS=1: after every GEMM call, wait for the device and raise if a bounded wait inside the
+# kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
+_DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")
+_GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k")
 launch_count = 0  # running total of kernels this process enqueued through the C ABI
 _event_log = None  # when a dict: name -> [(start_event, stop_event), ...] on the launching stream
 
@@ -113,6 +117,11 @@ def call(name: str, *args) -> None:
         rc = fn(*args)
     check(rc, name)
     launch_count += KERNELS_PER_CALL.get(name, 1)
+    if _DEBUG_STATUS and name in _GEMM_ENTRY_POINTS:
+        torch.cuda.synchronize()
+        code = gemm_status(reset=True)
+        if code != 0:
+            raise PtbError(f"{name}: a device-side wait ran out (status {code}); the output is incomplete")
 
 
 class record_kernel_times:

@@ -2,7 +2,7 @@
 // accumulator in tensor memory, per-128-K-block scale promotion in registers, bf16/fp16 epilogue.
 //
 // One persistent CTA per SM, 384 threads:
-//   warp 0      TMA producer (one lane): fills a 4-stage ring of {A 128x128, B 256x128} FP8 tiles,
+//   warp 0      TMA producer (one lane): fills a 3-stage (4 without output staging) ring of {A 128x128, B 256x128} FP8 tiles,
 //               128-byte swizzled, either K-major or MN-major (transposed operands need no copy).
 //   warp 1      MMA issuer (one lane): 4 x tcgen05.mma (M128 N256 K32) per stage.  With blockwise
 //               scales every 128-K block goes to one of two 256-column TMEM buffers with the
@@ -16,8 +16,6 @@
 // kernel records a status word, drains its own copies and leaves normally.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "ptb_common.cuh"
 
 namespace ptb {
@@ -28,24 +26,19 @@ constexpr int kABytes     = BM * BK;              // 16 KiB
 constexpr int kMaxStages  = 8;
 constexpr int kMaxAccBufs = 4;
 
-// Compile-time geometry of one tile width.
-//   BN = 256: eight promotion warps own 128 columns each, two 256-column TMEM buffers, 3 stages of
-//             48 KiB (4 stages without output staging when DEEP).  Used when scales are applied once
-//             per tile (tensorwise / rowwise): the TMEM drain is rare there.
-//   BN = 192: twelve promotion warps own 64 columns each, so a warp's whole slice of a partial product
-//             is fetched in one tensor-memory round trip and the buffer is handed back before any
-//             arithmetic.  Measured slower than BN = 256 (register-starved at 152 per thread); kept
-//             selectable for experiments.
-//   BN = 128: eight promotion warps own 64 columns each, four TMEM buffers (kept for experiments; one
-//             CTA per 128-wide tile is shared-memory-bandwidth bound).
+// Compile-time geometry.  The tile is 128 x 256: eight promotion warps own 128 columns each, two
+// 256-column TMEM buffers, 3 stages of 48 KiB.  (192- and 128-wide tiles were built and measured
+// slower on every shape -- 8192^3 blockwise: 2044 TFLOP/s at 256, 1558 at 192 with twelve promotion
+// warps, 1349 at 128 -- and are not compiled into the library.)
 // DEEP = 1 trades the output staging buffer for one more pipeline stage (plain stores in the epilogue).
 template <int BN, int DEEP> struct Geo {
-    static constexpr int kSliceCols   = BN == 256 ? 128 : 64;       // columns owned by one promotion warp
-    static constexpr int kEpiWarps    = 4 * (BN / kSliceCols);      // 8, 12, 8
+    static_assert(BN == 256, "only the 256-wide tile is built");
+    static constexpr int kSliceCols   = 128;                        // columns owned by one promotion warp
+    static constexpr int kEpiWarps    = 4 * (BN / kSliceCols);      // 8
     static constexpr int kThreads     = 128 + 32 * kEpiWarps;
-    static constexpr int kBBytes      = (BN == 192 ? 256 : BN) * BK; // MN-major B arrives in 128-column boxes
+    static constexpr int kBBytes      = BN * BK;
     static constexpr int kStageBytes  = kABytes + kBBytes;
-    static constexpr int kStages      = (BN == 128 ? 5 : 3) + DEEP;
+    static constexpr int kStages      = 3 + DEEP;
     static constexpr int kAccBufs     = 512 / BN;
     static constexpr int kChunks      = kSliceCols / 32;            // 32-column TMEM loads per partial
     static constexpr int kWarpCBytes  = 32 * kSliceCols * 2;        // staging of one warp's 32-row slab (16-bit out)
@@ -444,8 +437,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
     if (warp < 4) {
         // register split between the helper warpgroup and the two promotion warpgroups: the 1-D x 1-D
         // promotion needs every register it can get, the other modes leave more to the MMA issuer
-        if constexpr (kEpiWarps == 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-        else if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
@@ -460,14 +452,14 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     const uint32_t ph = (it / kStages) & 1;
                     if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1)) { ok = false; break; }
                     const uint32_t full = smem_u32(&ctl->full[s]);
-                    mbar_expect_tx(full, kABytes + ((BN == 192 && !args.b_mn) ? BN * BK : G_::kBBytes));
+                    mbar_expect_tx(full, kStageBytes);
                     const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kABytes;
                     const int k = t.k_row0 + kb * BK;
                     if (args.a_mn) tma_load_3d(sa, &args.tm_a, full, t.m0, k, 0);
                     else           tma_load_3d(sa, &args.tm_a, full, k, t.m0, 0);
                     if (args.b_mn) {
                         tma_load_3d(sb, &args.tm_b, full, t.n0, k, gb);
-                        if constexpr (BN >= 192) tma_load_3d(sb + 16384, &args.tm_b, full, t.n0 + 128, k, gb);
+                        tma_load_3d(sb + 16384, &args.tm_b, full, t.n0 + 128, k, gb); // MN-major boxes are 128 columns wide
                     } else {
                         tma_load_3d(sb, &args.tm_b, full, k, t.n0, gb);
                     }
@@ -503,10 +495,16 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     if (!mbar_wait(smem_u32(&ctl->full[s]), ph)) { ok = false; break; }
                     uint8_t *a_tile = smem + s * kStageBytes;
                     if (t.k_tail != 0 && kb == t.num_kb - 1) {
-                        // The last block of an unpadded group reaches into the next group's rows:
-                        // clear those contraction rows of the (MN-major) A tile so they add nothing.
-                        for (int off = t.k_tail * 128 + lane * 16; off < kABytes; off += 32 * 16)
-                            *reinterpret_cast<uint4 *>(a_tile + off) = make_uint4(0, 0, 0, 0);
+                        // The last block of an unpadded group reaches into the next group's rows (or
+                        // past the last group): clear those contraction rows in both MN-major operand
+                        // tiles, so that whatever bytes lie there -- FP8 NaN patterns included -- add
+                        // nothing.  A contraction row is 128 bytes in the A tile and in each of the two
+                        // 128-column halves of the B tile; the swizzle only permutes bytes inside a row.
+                        for (int off = t.k_tail * 128 + lane * 16; off < kABytes; off += 32 * 16) {
+                            *reinterpret_cast<uint4 *>(a_tile + off)                   = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4 *>(a_tile + kABytes + off)         = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4 *>(a_tile + kABytes + 16384 + off) = make_uint4(0, 0, 0, 0);
+                        }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     }
                     __syncwarp();
@@ -571,8 +569,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
             }
         }
     } else {
-        if constexpr (kEpiWarps == 12) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
-        else if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ================= promotion + epilogue warpgroups =================
         const int wg   = (warp - 4) >> 2;         // column slice of the tile this warp owns
@@ -671,25 +668,17 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         acc[(C) * 32 + 4 * j] = a0.x; acc[(C) * 32 + 4 * j + 1] = a0.y;                                         \
         acc[(C) * 32 + 4 * j + 2] = a1.x; acc[(C) * 32 + 4 * j + 3] = a1.y;                                     \
     }
-                if constexpr (kChunks == 4) {
-                    PTB_PROMOTE(v0, 0)
-                    tc_ld32(taddr + 64, v0);
-                    PTB_PROMOTE(v1, 1)
-                    tc_ld32(taddr + 96, v1);
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf])); // buffer may be overwritten now
-                    PTB_PROMOTE(v0, 2)
-                    PTB_PROMOTE(v1, 3)
-                } else {
-                    // the whole partial is in registers: hand the buffer back before doing any arithmetic
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
-                    PTB_PROMOTE(v0, 0)
-                    PTB_PROMOTE(v1, 1)
-                }
+                static_assert(kChunks == 4, "the promotion loop is written for four 32-column loads");
+                PTB_PROMOTE(v0, 0)
+                tc_ld32(taddr + 64, v0);
+                PTB_PROMOTE(v1, 1)
+                tc_ld32(taddr + 96, v1);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf])); // buffer may be overwritten now
+                PTB_PROMOTE(v0, 2)
+                PTB_PROMOTE(v1, 3)
 #undef PTB_PROMOTE
                 if constexpr (SCALE == kScaleBlock1D) {
                     __syncwarp(); // every lane has read its scales: the loader may refill the slot
@@ -734,10 +723,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     if (lane == 0) {
                         const int gc = (args.kind == kKindGroupedK) ? t.g : 0;
                         if (col0 < args.N) tma_store_3d(&args.tm_c, smem_u32(my_stage), col0, warp_row0, gc);
-                        if constexpr (kWgCols == 128) {
-                            if (col0 + 64 < args.N)
-                                tma_store_3d(&args.tm_c, smem_u32(my_stage + 4096), col0 + 64, warp_row0, gc);
-                        }
+                        if (col0 + 64 < args.N) tma_store_3d(&args.tm_c, smem_u32(my_stage + 4096), col0 + 64, warp_row0, gc);
                         tma_store_commit();
                     }
                     store_pending = true;
@@ -862,8 +848,7 @@ template <int BN, int DEEP> constexpr size_t smem_bytes() {
     return 1024 + (size_t) Geo<BN, DEEP>::kStages * Geo<BN, DEEP>::kStageBytes + Geo<BN, DEEP>::kCStageBytes +
            sizeof(SharedCtl);
 }
-static_assert(smem_bytes<256, 0>() <= 232448 && smem_bytes<128, 0>() <= 232448 && smem_bytes<256, 1>() <= 232448 &&
-                  smem_bytes<192, 0>() <= 232448,
+static_assert(smem_bytes<256, 0>() <= 232448 && smem_bytes<256, 1>() <= 232448,
               "shared memory budget of one CTA exceeded");
 
 template <int SCALE, typename OutT, int BN, int DEEP> int launch_bn(const GemmArgs &args, int grid, cudaStream_t st) {
@@ -882,8 +867,6 @@ template <int SCALE, typename OutT, int BN, int DEEP> int launch_bn(const GemmAr
 }
 
 template <int SCALE, typename OutT> int launch_one(const GemmArgs &args, int grid, cudaStream_t st) {
-    if (args.bn == 128) return launch_bn<SCALE, OutT, 128, 0>(args, grid, st);
-    if (args.bn == 192) return launch_bn<SCALE, OutT, 192, 0>(args, grid, st);
     return args.deep ? launch_bn<SCALE, OutT, 256, 1>(args, grid, st) : launch_bn<SCALE, OutT, 256, 0>(args, grid, st);
 }
 
@@ -898,9 +881,8 @@ template <int SCALE> int launch_scale(const GemmArgs &args, int out_dtype, int g
 
 int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cudaStream_t st) {
     // Tensorwise / rowwise scales keep the whole K loop in TMEM, so the epilogue is rare: spend the
-    // staging buffer on a fourth pipeline stage instead (measured +8 % on 8192^3).  PTB_GEMM_DEEP overrides.
-    const char *deep = getenv("PTB_GEMM_DEEP");
-    args.deep        = deep ? atoi(deep) : ((scale_mode == kScaleTensor || scale_mode == kScaleRow) && args.kind == kKindDense);
+    // staging buffer on a fourth pipeline stage instead (measured +8 % on 8192^3).
+    args.deep = ((scale_mode == kScaleTensor || scale_mode == kScaleRow) && args.kind == kKindDense) ? 1 : 0;
     int dev = 0, sms = 0;
     PTB_CUDA(cudaGetDevice(&dev));
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -914,18 +896,7 @@ int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cuda
     }
 }
 
-// Tile width.  PTB_GEMM_BN=128|192|256 overrides (tuning experiments).
-int choose_bn(int scale_mode) {
-    const char *e = getenv("PTB_GEMM_BN");
-    if (e) {
-        const int v = atoi(e);
-        if (v == 128 || v == 192 || v == 256) return v;
-    }
-    // Measured on 8192^3 blockwise: 256-wide 2044 TFLOP/s, 192-wide with twelve promotion warps 1558,
-    // 128-wide 1349 -- the narrower geometries stay selectable for experiments only.
-    (void) scale_mode;
-    return 256;
-}
+constexpr int kTileN = 256;
 
 int scale_mode_of(int granularity, int b_block_2d, int *mode) {
     switch (granularity) {
@@ -975,7 +946,7 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
     int rc = scale_mode_of(granularity, b_block_2d, &mode);
     if (rc) return rc;
     GemmArgs g{};
-    const int BN = choose_bn(mode);
+    const int BN = kTileN;
     g.bn         = BN;
     // A: [M,K] K-major, or [K,M] (trans_a) MN-major
     if (!trans_a) rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M, 1, (uint64_t) lda, (uint64_t) lda * M, BM);
@@ -1014,7 +985,7 @@ int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b,
     int rc = scale_mode_of(granularity, 1, &mode);
     if (rc) return rc;
     GemmArgs g{};
-    const int BN = choose_bn(mode);
+    const int BN = kTileN;
     g.bn         = BN;
     rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M_total, 1, (uint64_t) lda, (uint64_t) lda * M_total, BM);
     if (rc) return rc;
@@ -1052,7 +1023,7 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
                     G * cdiv<int64_t>(OUT_M, BM) * cdiv<int64_t>(OUT_N, 128) < (1ll << 31),
                 PTB_ERR_TOO_LARGE, "grouped_gemm_fp8_variable_k: problem too large");
     GemmArgs g{};
-    const int BN = choose_bn(mode);
+    const int BN = kTileN;
     g.bn         = BN;
     const uint64_t r = rows > 0 ? (uint64_t) rows : 1;
     rc = make_map(&g.tm_a, lhs, (uint64_t) OUT_M, r, 1, (uint64_t) ld_lhs, (uint64_t) ld_lhs * r, BK);

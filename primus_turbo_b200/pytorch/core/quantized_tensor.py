@@ -261,6 +261,26 @@ class QuantizedTensor(torch.Tensor):
             requires_grad=self.requires_grad,
         )
 
+    @staticmethod
+    def _view_data_and_scale_inv(tensor: "QuantizedTensor", target_shape, op):
+        """Apply ``op`` (``Tensor.view`` or ``Tensor.reshape``) to the payload.  The target keeps the
+        number of dimensions; the inverse scales are carried along unchanged, exactly as the reference
+        does for its non-MX formats (quantized_tensor.py:700-740 there), so a caller who reshapes
+        across a scaled axis owns the consequences."""
+        assert len(target_shape) == tensor.qdata.ndim
+        out_shape = torch.Size(target_shape)
+        if out_shape == tensor.shape:
+            return tensor._data, tensor._scale_inv, out_shape
+        return op(tensor._data, *target_shape), tensor._scale_inv, out_shape
+
+    def view(self, *shape) -> "QuantizedTensor":
+        """View without dequantising (autograd-aware)."""
+        return _ViewFunc.apply(self, _shape_arg(shape))
+
+    def reshape(self, *shape) -> "QuantizedTensor":
+        """Reshape without dequantising (autograd-aware)."""
+        return _ReshapeFunc.apply(self, _shape_arg(shape))
+
     @classmethod
     def _transpose(cls, t: "QuantizedTensor", dim0: int, dim1: int) -> "QuantizedTensor":
         """TENSORWISE: exact byte transpose.  Other granularities: dequantise and re-quantise the
@@ -318,6 +338,53 @@ class QuantizedTensor(torch.Tensor):
             f"QuantizedTensor(shape={tuple(self.shape)}, dtype={self._dest_dtype}, "
             f"granularity={self._granularity.name}, axis={self._quantized_axis})"
         )
+
+
+def _shape_arg(shape) -> Tuple[int, ...]:
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    return tuple(int(d) for d in shape)
+
+
+def _resolve_minus_one(shape: Tuple[int, ...], numel: int) -> Tuple[int, ...]:
+    if -1 not in shape:
+        return shape
+    known = 1
+    for d in shape:
+        if d != -1:
+            known *= d
+    return tuple(numel // max(known, 1) if d == -1 else d for d in shape)
+
+
+class _ViewFunc(torch.autograd.Function):
+    """View a QuantizedTensor without dequantising; the gradient is reshaped back
+    (quantized_tensor.py:838-858 in the reference)."""
+
+    @staticmethod
+    def forward(ctx, tensor: QuantizedTensor, shape: Tuple[int, ...]) -> QuantizedTensor:
+        ctx.shape = tensor.shape
+        shape = _resolve_minus_one(shape, tensor.numel())
+        data, sinv, out_shape = QuantizedTensor._view_data_and_scale_inv(tensor, shape, torch.Tensor.view)
+        return tensor._like(data, sinv, out_shape)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad.reshape(ctx.shape), None
+
+
+class _ReshapeFunc(torch.autograd.Function):
+    """Reshape a QuantizedTensor without dequantising (quantized_tensor.py:861-881 in the reference)."""
+
+    @staticmethod
+    def forward(ctx, tensor: QuantizedTensor, shape: Tuple[int, ...]) -> QuantizedTensor:
+        ctx.shape = tensor.shape
+        shape = _resolve_minus_one(shape, tensor.numel())
+        data, sinv, out_shape = QuantizedTensor._view_data_and_scale_inv(tensor, shape, torch.Tensor.reshape)
+        return tensor._like(data, sinv, out_shape)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad.reshape(ctx.shape), None
 
 
 class QuantizedTensorPair(NamedTuple):

@@ -79,3 +79,72 @@ def test_float8_linear_conversion_mechanics():
     assert nb.bias is None and nb.config.granularity == ScalingGranularity.TENSORWISE
     with pytest.raises(AssertionError):
         Float8Linear.from_float(torch.nn.ReLU())
+
+
+def _cpu_qt(shape=(4, 6), gran=None, requires_grad=False):
+    import torch
+
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
+
+    data = torch.arange(shape[0] * shape[1], dtype=torch.uint8).reshape(shape).view(torch.float8_e4m3fn)
+    return QuantizedTensor(
+        data, torch.full((), 0.5), shape=data.shape, orig_dtype=torch.bfloat16, dest_dtype=torch.float8_e4m3fn,
+        granularity=gran or ScalingGranularity.TENSORWISE, quantized_axis=-1, requires_grad=requires_grad,
+    )
+
+
+def test_quantized_tensor_view_and_reshape_keep_payload_and_metadata():
+    """view / reshape move the FP8 payload without dequantising, keep the scale and the wrapper's
+    metadata, and send the gradient back in the original shape
+    (primus_turbo/pytorch/core/quantized_tensor.py:700-740,838-881)."""
+    import torch
+
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
+
+    q = _cpu_qt(requires_grad=True)
+    for v in (q.view(6, 4), q.view((3, 8)), q.reshape(-1, 12), q.reshape(2, -1)):
+        assert isinstance(v, QuantizedTensor) and v.qdata.shape == v.shape and v.numel() == 24
+        assert torch.equal(v.qdata.view(torch.uint8).reshape(-1), q.qdata.view(torch.uint8).reshape(-1))
+        assert v.scale_inv is q.scale_inv and v.granularity == q.granularity and v.real_dtype == q.real_dtype
+        assert v.dtype == torch.bfloat16 and v.quantized_axis == q.quantized_axis
+    same = q.view(4, 6)
+    assert same.qdata.data_ptr() == q.qdata.data_ptr()
+    v = q.view(6, 4)
+    assert v.grad_fn is not None
+    (gin,) = v.grad_fn.apply(torch.ones(6, 4))[:1]
+    assert gin.shape == (4, 6)
+    import pytest
+
+    with pytest.raises(AssertionError):
+        q.view(24)  # the number of dimensions is kept, as in the reference
+
+
+def test_quantized_tensor_flatten_unflatten_round_trip():
+    """__tensor_flatten__ / __tensor_unflatten__ (what torch.compile and FSDP use to take the wrapper
+    apart and rebuild it) reproduce payload, scales and every piece of metadata."""
+    import torch
+
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
+
+    data = torch.zeros(8, 16, dtype=torch.float8_e5m2)
+    lens = torch.tensor([3, 5])
+    offs = torch.tensor([0, 3, 8])
+    q = QuantizedTensor(
+        data, torch.ones(8, 1), shape=data.shape, orig_dtype=torch.float16, dest_dtype=torch.float8_e5m2,
+        granularity=ScalingGranularity.ROWWISE, block_size=None, scaling_recipe=ScalingRecipe(), quantized_axis=-1,
+        group_lens=lens, group_offs=offs, orig_group_lens=lens, orig_group_offs=offs, is_grouped_tensor=True,
+    )
+    names, meta = q.__tensor_flatten__()
+    assert names[:2] == ["_data", "_scale_inv"] and set(names[2:]) == {
+        "_orig_group_lens", "_orig_group_offs", "_group_lens", "_group_offs"}
+    r = QuantizedTensor.__tensor_unflatten__({n: getattr(q, n) for n in names}, meta, q.shape, q.stride())
+    assert r.shape == q.shape and r.dtype == torch.float16 and r.real_dtype == torch.float8_e5m2
+    assert r.granularity == ScalingGranularity.ROWWISE and r.quantized_axis == -1 and r._is_grouped_tensor
+    assert r.qdata is q.qdata and r.scale_inv is q.scale_inv and r.group_lens is lens and r.group_offs is offs
+    plain = _cpu_qt()
+    names, meta = plain.__tensor_flatten__()
+    assert names == ["_data", "_scale_inv"]
+    r = QuantizedTensor.__tensor_unflatten__({n: getattr(plain, n) for n in names}, meta, plain.shape, None)
+    assert r.group_lens is None and not r._is_grouped_tensor
