@@ -155,6 +155,34 @@ int ptb_group_offs(const int64_t *group_lens, int64_t G, int64_t *group_offs, pt
 int ptb_transpose_2d_u8(const void *in, int64_t B, int64_t M, int64_t N, void *out,
                         ptb_stream_t stream);
 
+/* ------------------------------------------------------------------ row movement ------------- */
+/* Copies row segments from src_base to up to 16 destination buffers in one launch:
+ *   segments: device int64 [nseg][4] = {first source row, first destination row, rows,
+ *   destination index}; dst_bases: host array of n_ranks device pointers (peer memory mapped into this
+ *   process, or local memory); rows are row_bytes bytes (a multiple of 16; all bases 16-byte aligned).
+ * This is the expert-parallel dispatch / combine of ranks on one node: every rank writes its rows
+ * straight to their expert-major position in the owner's buffer with plain stores over NVLink.  The
+ * kernel waits on nothing -- the callers order themselves with a collective afterwards.  A segment
+ * naming a destination outside [0, n_ranks) is skipped and recorded (ptb_copy_segments_status).
+ * num_ctas <= 0 uses one CTA per SM.  At most 8192 segments.
+ * Stands where the reference calls its DeepEP port's dispatch / combine
+ * (primus_turbo/pytorch/ops/moe/moe_dispatch_combine.py:20-101,
+ * primus_turbo/pytorch/kernels/moe/moe_dispatch_combine_impl.py). */
+int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
+                      const int64_t *segments, int64_t nseg, int64_t row_bytes, int num_ctas,
+                      ptb_stream_t stream);
+
+/* Reads (and optionally clears) the flag a copy sets when its segment table named a bad
+ * destination.  Synchronises with the device.  No counterpart in the reference. */
+int ptb_copy_segments_status(int *status, int reset);
+
+/* out[i, :] = in[index[i], :] for n_out rows of row_bytes bytes (a multiple of 16); an index outside
+ * [0, n_in) writes a zero row.  The row gather of the MoE token permutation
+ * (csrc/kernels/moe_permute/moe_permute.cu, primus_turbo/pytorch/ops/moe/permutation.py:281-369:
+ * ``inp.index_select(0, sorted_indices)``). */
+int ptb_gather_rows(const void *in, const int64_t *index, int64_t n_out, int64_t n_in,
+                    int64_t row_bytes, void *out, ptb_stream_t stream);
+
 /* ------------------------------------------------------------------ GEMM --------------------- */
 /* C[M,N] = op(A)[M,K] . op(B)[K,N], FP8 operands, fp32 accumulation, c_dtype output.
  *   a: [M,K] (trans_a = 0, lda = row pitch in elements) or [K,M] (trans_a = 1)

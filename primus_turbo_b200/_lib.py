@@ -52,6 +52,9 @@ _PROTOS = {
     "ptb_grouped_gemm_fp8": [_P, _I, _L, _P, _I, _I, _P, _I, _L, _P, _L, _L, _L, _L, _I, _P, _L, _L, _P, _L, _L, _L,
                              _I, _P],
     "ptb_grouped_gemm_fp8_variable_k": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _I, _P],
+    "ptb_copy_segments": [_P, _P, _I, _P, _L, _L, _I, _P],
+    "ptb_copy_segments_status": [ctypes.POINTER(c_int), _I],
+    "ptb_gather_rows": [_P, _P, _L, _L, _L, _P, _P],
     "ptb_gemm_status": [ctypes.POINTER(c_int), _I],
     "ptb_gemm_wait_selftest": [_P],
 }
@@ -93,7 +96,7 @@ def check(rc: int, what: str) -> None:
 # kernels enqueued by one successful call of each entry point (memset nodes not counted)
 KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_rowwise_noalloc": 2,
                     "ptb_quant_fp8_segment_row_col": 2,
-                    "ptb_gemm_status": 0}
+                    "ptb_gemm_status": 0, "ptb_copy_segments_status": 0}
 # PTB_DEBUG_STATUS=1: after every GEMM call, wait for the device and raise if a bounded wait inside the
 # kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
 _DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")
@@ -162,6 +165,12 @@ def require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise PtbError("tensors must live on a CUDA device: this library has no CPU path")
+
+
+def copy_segments_status(reset: bool = True) -> int:
+    out = c_int(0)
+    check(lib.ptb_copy_segments_status(ctypes.byref(out), 1 if reset else 0), "ptb_copy_segments_status")
+    return out.value
 
 
 def gemm_status(reset: bool = True) -> int:

@@ -25,7 +25,8 @@ import torch.distributed as dist
 
 __all__ = [
     "ExchangePlan", "build_exchange_plan", "expert_parallel_apply", "ep_grouped_gemm_fp8", "BlockwiseLocalSteps",
-    "SharedCountsBoard",
+    "SharedCountsBoard", "PeerPlan", "build_peer_plan", "expert_parallel_apply_peer", "balanced_expert_order",
+    "load_imbalance",
 ]
 
 
@@ -248,6 +249,15 @@ class _AllToAllRows(torch.autograd.Function):
         return gx, None, None, None
 
 
+def _gather(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """Row gather: the library's kernel for CUDA rows of 16-byte multiples, torch otherwise (CPU tests)."""
+    if x.is_cuda and x.dim() == 2 and (x.shape[1] * x.element_size()) % 16 == 0:
+        from primus_turbo_b200.pytorch.kernels.quantization_impl import gather_rows
+
+        return gather_rows(x, index)
+    return x.index_select(0, index)
+
+
 class _PermuteRows(torch.autograd.Function):
     """y = x[index] for a permutation ``index`` with inverse ``inverse``.  Both directions are row
     gathers (``index_select``): a gather streams at HBM speed, a scatter through ``index_copy_``
@@ -256,12 +266,12 @@ class _PermuteRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, index, inverse):
         ctx.save_for_backward(index, inverse)
-        return x.index_select(0, index)
+        return _gather(x, index)
 
     @staticmethod
     def backward(ctx, g):
         index, inverse = ctx.saved_tensors
-        return g.index_select(0, inverse), None, None
+        return _gather(g, inverse), None, None
 
 
 def expert_parallel_apply(
@@ -475,3 +485,84 @@ def ep_grouped_gemm_fp8(
         return grouped_gemm_fp8(rows, w_local, group_lens, trans_b=trans_b, config=config)
 
     return expert_parallel_apply(x_local, counts_local, local_fn, group, plan)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Peer-memory exchange (one node): rows are written straight to their expert-major position
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class PeerPlan:
+    """Per-step plan of the peer-memory exchange (``peer_exchange.py``): the host-side tables plus their
+    device copies (uploaded as one copy from pinned memory)."""
+
+    tables: "object"  # peer_exchange.SegmentTables (host)
+    seg_dev: tuple  # (dispatch [E,4], combine [E,4]) int64 on the device
+    group_lens: torch.Tensor  # [E_local] int64 on the device
+    counts_matrix: torch.Tensor  # [world, E] int64 on the host
+
+
+def build_peer_plan(counts_host: torch.Tensor, host_group, device, group: Optional[dist.ProcessGroup] = None) -> PeerPlan:
+    """Gather every rank's host-side routing counts (``SharedCountsBoard`` or a CPU process group) and
+    derive both exchanges' row segments; nothing here waits on the device."""
+    from primus_turbo_b200.pytorch.dist.peer_exchange import segment_tables
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    E = counts_host.numel()
+    if isinstance(host_group, SharedCountsBoard):
+        matrix = host_group.all_gather_counts(counts_host)
+    else:
+        flat = torch.empty(world * E, dtype=torch.int64)
+        dist.all_gather_into_tensor(flat, counts_host.to(torch.int64).contiguous(), group=host_group)
+        matrix = flat.view(world, E)
+    tables = segment_tables(matrix, rank)
+    parts = [tables.dispatch.reshape(-1), tables.combine.reshape(-1), tables.group_lens]
+    numel = sum(p.numel() for p in parts)
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        staging = _pinned_pool.take(numel)
+        torch.cat(parts, out=staging[:numel])
+        packed = staging[:numel].to(dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+        _pinned_pool.give_back(staging, ev)
+    else:
+        packed = torch.cat(parts)
+    d, c, lens = torch.split(packed, [p.numel() for p in parts])
+    return PeerPlan(tables, (d.view(-1, 4), c.view(-1, 4)), lens, matrix)
+
+
+def expert_parallel_apply_peer(x_local: torch.Tensor, local_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+                               exchange, plan: PeerPlan) -> torch.Tensor:
+    """``expert_parallel_apply`` over peer-mapped buffers: dispatch and combine are one copy kernel each,
+    rows arrive in expert-major order (no permutation pass), results are bit-identical to the
+    all-to-all form."""
+    from primus_turbo_b200.pytorch.dist.peer_exchange import peer_combine, peer_dispatch
+
+    rows = peer_dispatch(x_local, exchange, plan.tables, plan.seg_dev)
+    y = local_fn(rows, plan.group_lens)
+    return peer_combine(y, exchange, plan.tables, plan.seg_dev)
+
+
+def balanced_expert_order(expected_load: torch.Tensor, world: int) -> torch.Tensor:
+    """Placement of ``E`` experts on ``world`` ranks, ``E / world`` each, that evens out the rows per rank:
+    experts in decreasing order of expected load go to the least-loaded rank that still has room
+    (longest-processing-time-first).  Returns ``order`` ([E] int64): position ``p`` of the placement holds
+    global expert ``order[p]``, rank ``r`` owns positions ``[r*E/world, (r+1)*E/world)``.  The exchange
+    itself always shards positions contiguously: a caller that wants this placement sorts its rows (and
+    orders its counts and weights) by position instead of by global expert id."""
+    load = expected_load.to(torch.float64).flatten()
+    E = load.numel()
+    assert E % world == 0
+    e_loc = E // world
+    totals, members = [0.0] * world, [[] for _ in range(world)]
+    for e in torch.argsort(load, descending=True, stable=True).tolist():
+        r = min((r for r in range(world) if len(members[r]) < e_loc), key=lambda r: (totals[r], r))
+        members[r].append(e)
+        totals[r] += float(load[e])
+    return torch.tensor([e for m in members for e in sorted(m)], dtype=torch.int64)
+
+
+def load_imbalance(load: torch.Tensor, world: int) -> float:
+    """max over ranks / mean over ranks of the rows a contiguous sharding of ``load`` gives each rank."""
+    per_rank = load.to(torch.float64).view(world, -1).sum(1)
+    return float(per_rank.max() * world / per_rank.sum()) if float(per_rank.sum()) > 0 else 1.0

@@ -1,0 +1,202 @@
+"""Single-node row exchange over peer-mapped buffers: the expert-parallel dispatch and combine as ONE
+copy kernel per direction that writes every row straight to its final, expert-major position in the
+destination GPU's memory (plain stores over NVLink / NVSwitch), instead of an all-to-all into a
+staging buffer followed by a permutation pass on the receiver.
+
+The reference wraps ``grouped_gemm_fp8`` between a token dispatch and combine backed by its DeepEP
+port (primus_turbo/pytorch/ops/moe/moe_dispatch_combine.py:20-101); this module is the same pair of
+steps for ranks that share one machine.
+
+How it works
+* Every rank allocates its receive regions with torch and publishes them to the other ranks of the
+  node as CUDA IPC handles (``torch.multiprocessing.reductions.reduce_tensor`` -> one object
+  all-gather over a CPU group); each rank opens the others' handles once and keeps raw pointers.
+* The routing counts of all ranks ([world, E]) give, on the host and for both directions, one row
+  segment per (rank, expert): first source row, first destination row, row count, destination rank
+  (``segment_tables``).  ``ptb_copy_segments`` (csrc/ptb_exchange.cu) performs all copies of a rank
+  in one launch.
+* The copy kernel waits on nothing.  Ranks are ordered by a one-element NCCL all-reduce after each
+  exchange: a rank reads a region only after that collective, and a region is overwritten at the
+  earliest one collective after its reader consumed it (each region is written once per step).
+* No kernel here loads from peer memory through TMA, and nothing uses cluster multicast.
+
+The CPU tests drive the same plan and bookkeeping with shared-memory tensors and a copy loop of their
+own (``copy_fn``); the product path has no CPU implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["SegmentTables", "segment_tables", "PeerExchange", "peer_dispatch", "peer_combine"]
+
+
+@dataclass
+class SegmentTables:
+    """Row segments of one rank for both directions, int64 ``[nseg, 4]`` each: first source row, first
+    destination row, rows, destination rank."""
+
+    dispatch: torch.Tensor  # my rows (sorted by expert) -> the owners' expert-major buffers
+    combine: torch.Tensor  # my expert-major rows -> the source ranks' original positions
+    group_lens: torch.Tensor  # [E_local] rows per local expert after the dispatch
+    rows_in: int  # rows this rank holds before the dispatch (= after the combine)
+    rows_out: int  # rows this rank holds after the dispatch
+
+
+def segment_tables(counts_matrix: torch.Tensor, rank: int) -> SegmentTables:
+    """Index arithmetic of both exchanges from the host copy of the ``[world, E]`` count matrix
+    (``counts_matrix[s, e]`` = rows rank ``s`` routes to expert ``e``; experts sharded contiguously,
+    expert ``e`` on rank ``e // (E / world)``; every rank's rows are sorted by expert)."""
+    C = counts_matrix.to(torch.int64)
+    world, E = C.shape
+    assert E % world == 0
+    e_loc = E // world
+    total = C.sum(0)  # rows per expert over all sources
+    blk = total.view(world, e_loc)
+    start_in_owner = (blk.cumsum(1) - blk).reshape(E)  # first row of expert e in its owner's buffer
+    before_src = C.cumsum(0) - C  # [s, e]: rows of expert e that come from sources below s
+    own_off = C.cumsum(1) - C  # [s, e]: first row of expert e in rank s's own (sorted) rows
+    experts = torch.arange(E)
+    dispatch = torch.stack(
+        [own_off[rank], start_in_owner + before_src[rank], C[rank], experts // e_loc], dim=1
+    ).contiguous()
+    mine = experts[rank * e_loc : (rank + 1) * e_loc]
+    # (local expert, source) pairs in expert-major order
+    src_row = (start_in_owner[mine].unsqueeze(1) + before_src[:, mine].t()).reshape(-1)
+    dst_row = own_off[:, mine].t().reshape(-1)
+    rows = C[:, mine].t().reshape(-1)
+    dst_rank = torch.arange(world).repeat(e_loc)
+    combine = torch.stack([src_row, dst_row, rows, dst_rank], dim=1).contiguous()
+    return SegmentTables(dispatch, combine, total[mine].contiguous(), int(C[rank].sum()), int(total[mine].sum()))
+
+
+def _device_copy(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row_bytes: int, num_ctas: int) -> None:
+    from primus_turbo_b200 import _lib
+
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with torch.cuda.device(src.device):
+        _lib.call("ptb_copy_segments", src.data_ptr(), arr, len(dst_ptrs), segs.data_ptr(), segs.shape[0], row_bytes,
+                  num_ctas, torch.cuda.current_stream(src.device).cuda_stream)
+
+
+def _export_cuda_ipc(t: torch.Tensor):
+    from torch.multiprocessing.reductions import reduce_tensor
+
+    return reduce_tensor(t)
+
+
+def _import_cuda_ipc(handle):
+    fn, args = handle
+    return fn(*args)
+
+
+class PeerExchange:
+    """Receive regions of every rank of one node, mapped into this process, plus the ordering collective.
+
+    ``capacity_rows``: most rows a rank may receive in one dispatch (a plan that needs more raises).
+    Regions are created on first use, keyed by (direction, row width in bytes, forward / backward pass); creation is collective
+    (every rank must reach it in the same order, which the symmetric call sequence of a training step
+    guarantees).  ``host_group`` carries the handle exchange (a CPU group); ``group`` the ordering
+    collective (NCCL on GPUs).  ``copy_fn`` / ``alloc_fn`` replace the device pieces in CPU tests.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup], host_group: Optional[dist.ProcessGroup], device,
+                 capacity_rows: int, local_rows: int, copy_fn: Optional[Callable] = None,
+                 alloc_fn: Optional[Callable] = None, num_ctas: int = 0, export_fn: Optional[Callable] = None,
+                 import_fn: Optional[Callable] = None):
+        self.group, self.host_group = group, host_group
+        self.device = torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.capacity_rows, self.local_rows = int(capacity_rows), int(local_rows)
+        self.num_ctas = num_ctas
+        self._copy = copy_fn or _device_copy
+        self._alloc = alloc_fn or (lambda nbytes: torch.empty(nbytes, dtype=torch.uint8, device=self.device))
+        # how a region is published to / opened by the other ranks: for CUDA memory, torch's IPC handle
+        # (plain picklable values: device index, cudaIpcMemHandle bytes, sizes)
+        self._export = export_fn or _export_cuda_ipc
+        self._import = import_fn or _import_cuda_ipc
+        self._regions: Dict[Tuple[str, int, str], Tuple[torch.Tensor, List, List[int]]] = {}
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ---- regions ---------------------------------------------------------------------------------
+    def _region(self, direction: str, row_bytes: int, phase: str = "fwd"):
+        key = (direction, row_bytes, phase)
+        if key not in self._regions:
+            rows = self.capacity_rows if direction == "dispatch" else self.local_rows
+            local = self._alloc(max(rows, 1) * row_bytes)
+            handles: List = [None] * self.world
+            dist.all_gather_object(handles, self._export(local), group=self.host_group)
+            views, ptrs = [], []
+            for r, h in enumerate(handles):
+                t = local if r == self.rank else self._import(h)
+                views.append(t)  # keeps the mapping alive
+                ptrs.append(t.data_ptr())
+            self._regions[key] = (local, views, ptrs)
+        return self._regions[key]
+
+    # ---- the two exchanges ------------------------------------------------------------------------
+    def order(self) -> None:
+        """Stream-ordered rendezvous of all ranks (one-element all-reduce; the host is not blocked)."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self) -> None:
+        """Drop the mappings of the other ranks' regions (call before the process group is destroyed, so
+        that every rank releases its peers' memory while they still exist)."""
+        self._regions.clear()
+
+    def push(self, src: torch.Tensor, segs: torch.Tensor, direction: str, rows_received: int,
+             phase: str = "fwd") -> torch.Tensor:
+        """Copy ``src``'s row segments into every rank's region for ``direction`` and return this rank's
+        region viewed as ``[rows_received, width]`` (valid once ``order()`` has been enqueued, until
+        the next ``push`` of the same direction, width and phase).  Forward and backward passes use
+        separate regions (``phase``), so rows dispatched in a forward pass stay intact through the
+        matching backward pass -- a local function may keep them for its gradient -- and are replaced
+        by the next forward pass: one step in flight at a time."""
+        assert src.dim() == 2 and src.is_contiguous()
+        row_bytes = src.shape[1] * src.element_size()
+        limit = self.capacity_rows if direction == "dispatch" else self.local_rows
+        if rows_received > limit:
+            raise RuntimeError(f"{direction}: {rows_received} rows arrive at rank {self.rank} but the region holds {limit}")
+        local, _, ptrs = self._region(direction, row_bytes, phase)
+        if segs.shape[0] and src.shape[0]:
+            self._copy(src, ptrs, segs, row_bytes, self.num_ctas)
+        # `.data`: a tensor over the same bytes with its own version counter -- the region is rewritten by
+        # later exchanges (by kernels of other ranks), which autograd must not mistake for an in-place edit
+        return local.data[: rows_received * row_bytes].view(src.dtype).view(rows_received, src.shape[1])
+
+
+class _PeerMove(torch.autograd.Function):
+    """One exchange; its gradient is the opposite exchange over the same segments.  Results that leave
+    this module for the caller (the combined output, the gradient of the dispatched input) are copied
+    out of the region; results consumed at once by the local grouped GEMM are views of it."""
+
+    @staticmethod
+    def forward(ctx, x, ex: PeerExchange, fwd_segs, bwd_segs, direction, rows_fwd, rows_bwd):
+        ctx.ex, ctx.bwd_segs, ctx.rows_bwd = ex, bwd_segs, rows_bwd
+        ctx.bwd_direction = "combine" if direction == "dispatch" else "dispatch"
+        out = ex.push(x.contiguous(), fwd_segs, direction, rows_fwd)
+        ex.order()
+        return out.clone() if direction == "combine" else out
+
+    @staticmethod
+    def backward(ctx, g):
+        ex = ctx.ex
+        out = ex.push(g.contiguous(), ctx.bwd_segs, ctx.bwd_direction, ctx.rows_bwd, phase="bwd")
+        ex.order()
+        return (out.clone() if ctx.bwd_direction == "combine" else out), None, None, None, None, None, None
+
+
+def peer_dispatch(x_local: torch.Tensor, ex: PeerExchange, tables: SegmentTables, seg_dev: Tuple[torch.Tensor, torch.Tensor]):
+    """Rows sorted by global expert -> this rank's experts' rows in expert-major order (a view of the
+    receive region: consume it before the next dispatch of the same width)."""
+    return _PeerMove.apply(x_local, ex, seg_dev[0], seg_dev[1], "dispatch", tables.rows_out, tables.rows_in)
+
+
+def peer_combine(y: torch.Tensor, ex: PeerExchange, tables: SegmentTables, seg_dev: Tuple[torch.Tensor, torch.Tensor]):
+    """Expert-major result rows -> back to the rank and position their input rows came from."""
+    return _PeerMove.apply(y, ex, seg_dev[1], seg_dev[0], "combine", tables.rows_in, tables.rows_out)

@@ -255,3 +255,18 @@ def transpose_2d_fp8(x: torch.Tensor) -> torch.Tensor:
             "ptb_transpose_2d_u8", ptr(xc), B, M, N, ptr(out), stream_of(x),
         )
     return out
+
+
+def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``out[i] = x[index[i]]`` over the rows of a 2-D tensor whose rows are a multiple of 16 bytes (the row
+    gather of the MoE token permutation, ``inp.index_select(0, sorted_indices)`` in
+    primus_turbo/pytorch/ops/moe/permutation.py:281-369); an index outside ``[0, rows)`` gives a zero row."""
+    require_cuda(x, index)
+    assert x.dim() == 2 and index.dim() == 1 and index.dtype == torch.int64
+    xc = x.contiguous()
+    row_bytes = xc.shape[1] * xc.element_size()
+    out = torch.empty((index.numel(), xc.shape[1]), dtype=xc.dtype, device=xc.device)
+    with torch.cuda.device(x.device):
+        _lib.call("ptb_gather_rows", ptr(xc), ptr(index.contiguous()), index.numel(), xc.shape[0], row_bytes, ptr(out),
+                  stream_of(x))
+    return out

@@ -18,6 +18,7 @@ from primus_turbo_b200.pytorch.core.low_precision import (
     Float8QuantConfig,
     Format,
     ScalingGranularity,
+    ScalingRecipe,
     float8_e4m3,
     float8_e5m2,
 )
@@ -37,6 +38,8 @@ from primus_turbo_b200.pytorch.kernels.custom_ops import (
 from primus_turbo_b200.pytorch.kernels.gemm_impl import group_offs_from_lens
 
 __all__ = ["grouped_gemm_fp8"]
+
+_WEIGHT_RECIPE = ScalingRecipe(use_2d_block=True)  # how BLOCKWISE weights are quantised (128x128 blocks)
 
 
 def _get_fp8_dtype(format: Format, is_fwd_stage: bool):
@@ -63,11 +66,24 @@ class FP8GroupedGemmBlockFunc(torch.autograd.Function):
         assert group_lens.size(0) == b.size(0), "group_lens size must match b size(0)."
         assert out_dtype in [torch.float16, torch.bfloat16]
         dt = _get_fp8_dtype(config.format, True)
+        assert not isinstance(a, QuantizedTensor), (
+            "BLOCKWISE activations are quantised inside grouped_gemm_fp8 (their column copy depends on the groups)"
+        )
         # one read of a -> 1x128 row copy (forward) + segment-padded 128x1 column copy (wgrad)
         a_row, a_col, a_s_row, a_s_col, _, _ = quant_fp8_blockwise_segment_m_row_col_impl(
             _contig(a), dt, config.block_size, group_lens, group_offs
         )
-        b8, b_s = quant_fp8_blockwise_for_weight_impl(b, dt, config.block_size)
+        if isinstance(b, QuantizedTensor):
+            # A weight quantised ahead of time (create_quantized_weight): 128x128 blocks, used as stored by
+            # forward and dgrad alike, so the 3-bytes-per-element re-quantisation of every forward goes away.
+            # The reference accepts pre-quantised weights for its tensorwise / rowwise grouped paths only
+            # (ops/grouped_gemm_fp8.py:886-889 there); this is the same hook extended to BLOCKWISE.
+            assert not b._is_grouped_tensor, "B QuantizedTensor input must not be a grouped tensor"
+            check_quantized_tensor(b, config, scaling_recipe=_WEIGHT_RECIPE)
+            assert b.real_dtype == dt, f"pre-quantised weight is {b.real_dtype}, the config asks for {dt}"
+            b8, b_s = b.qdata, b.scale_inv
+        else:
+            b8, b_s = quant_fp8_blockwise_for_weight_impl(b, dt, config.block_size)
         out = grouped_gemm_fp8_impl(
             a_row, b8, a_s_row, b_s, group_lens, group_offs, trans_a=False, trans_b=trans_b, out_dtype=out_dtype,
             granularity=config.granularity.value, num_cu=num_cu,
@@ -230,5 +246,7 @@ def grouped_gemm_fp8(
             a_data, b_data, a_data_t, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu
         )
     if config.granularity == ScalingGranularity.BLOCKWISE:
-        return FP8GroupedGemmBlockFunc.apply(a, b, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
+        # raw activations; the weight may be raw or pre-quantised (the pair's forward member: forward
+        # and dgrad read the same 128x128-block payload)
+        return FP8GroupedGemmBlockFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

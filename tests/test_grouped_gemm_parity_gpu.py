@@ -223,3 +223,48 @@ def test_llama70b_out_proj_rowwise_fwd_dgrad_wgrad_sampled():
     rows_n = torch.arange(0, n, 163, device=DEV)
     ref = (gq_t[:, rows_n].float() * g_s_t[:, rows_n]).t() @ (xq_t.float() * x_s_t)
     assert O.rel_frobenius(ref.cpu(), dw[rows_n].float().cpu()) <= FROB_TOL
+
+
+# ---- weights quantised ahead of time ----------------------------------------------------------------------
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_cached_blockwise_weight_is_bit_identical_to_the_raw_path(trans_b):
+    """create_quantized_weight once, then grouped_gemm_fp8 / gemm_fp8 on the cached payload: the payload
+    equals a fresh quantisation byte for byte, and out, grad_a and grad_w are bit-identical to the
+    path that re-quantises the raw weight in every forward
+    (primus_turbo/pytorch/core/quantized_tensor.py:884-956 in the reference)."""
+    from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensorPair, create_quantized_weight
+    from primus_turbo_b200.pytorch.ops import gemm_fp8, grouped_gemm_fp8
+
+    cfg = Float8QuantConfig(granularity=G.BLOCKWISE, block_size=128)
+    g = gen(31)
+    lens = torch.tensor([200, 0, 300, 77, 1], dtype=torch.int64, device=DEV)
+    m, n, k, E = int(lens.sum()), 512, 640, 5
+    a = randn(g, m, k).to(DEV)
+    w = (randn(g, E, n, k, scale=0.02) if trans_b else randn(g, E, k, n, scale=0.02)).to(DEV)
+    go = randn(g, m, n, scale=1e-3).to(DEV)
+    qw, qw_t = create_quantized_weight(w.clone().requires_grad_(True), E4, cfg, need_weight_transpose_cache=True)
+    fresh_q, fresh_s = quant_fp8_blockwise_for_weight_impl(w, E4)
+    assert torch.equal(qw.qdata.view(torch.uint8), fresh_q.view(torch.uint8))
+    assert torch.equal(qw.scale_inv.view(torch.int32), fresh_s.view(torch.int32))
+    assert qw.shape == w.shape and qw.dtype == torch.bfloat16 and qw.requires_grad
+
+    def run(weight):
+        aa = a.clone().requires_grad_(True)
+        ww = weight if not torch.is_tensor(weight) or weight.requires_grad else weight.clone().requires_grad_(True)
+        out = grouped_gemm_fp8(aa, ww, lens, trans_b=trans_b, config=cfg)
+        leaf = ww.data if isinstance(ww, QuantizedTensorPair) else ww
+        ga, gw = torch.autograd.grad(out, (aa, leaf), go)
+        return out.detach(), ga, gw
+
+    base = run(w)
+    for cached in (qw, QuantizedTensorPair(qw, qw_t), QuantizedTensorPair(qw)):
+        got = run(cached)
+        for x, y in zip(base, got):
+            assert x.shape == y.shape and torch.equal(x, y)
+    _status_ok()
+    # dense op, same hook
+    qd, _ = create_quantized_weight(w[0], E4, cfg)
+    a2 = a[:256].contiguous()
+    assert torch.equal(gemm_fp8(a2, qd, trans_b=trans_b, out_dtype=torch.bfloat16, config=cfg),
+                       gemm_fp8(a2, w[0], trans_b=trans_b, config=cfg))
