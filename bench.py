@@ -1,20 +1,28 @@
 #!/usr/bin/env python
-"""Benchmark of the FP8 grouped-GEMM hot path (blockwise scales, DeepSeek-V3 expert shape).
+"""Benchmark of the FP8 quantise / GEMM / grouped-GEMM hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--config c1|c2|c3|c4|c5] [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" is one pass of the hot path over one batch of synthetic routed rows, through the public
-op ``grouped_gemm_fp8`` exactly as a caller runs it: activation quantise (1x128 row copy +
-segment-padded 128x1 column copy), weight quantise (128x128 tiles, redone every forward as the
-reference does), forward grouped GEMM, grad-out quantise, dgrad grouped GEMM, wgrad variable-K
-grouped GEMM.  FLOPs counted are the algorithmic 3 x 2*M*N*K only.
+One "step" is one pass of the hot path over one batch of synthetic input, through the public ops
+exactly as a caller runs them.  FLOPs counted are the algorithmic 2*M*N*K per GEMM only.
 
-Workload: 256 experts, hidden 7168, gate+up N=4096, 65536 routed rows, per-expert counts drawn from
-a multinomial over softmax(N(0,1) logits), seed 0; bf16 inputs, e4m3 payloads, fp32 scales.
-With N > 1 ranks the experts are sharded contiguously (256/N per GPU), the 65536 rows start evenly
-split over the ranks and travel to their expert's owner with an NCCL all-to-all (strong scaling).
-The per-step routing counts are gathered on the host through a shared-memory board (``--plan host``,
-default) or on the device (``--plan device``: NCCL gather plus one host read of the split sizes).
+  c4 (default, the headline): blockwise FP8 grouped GEMM at the DeepSeek-V3 expert shape -- 256 experts,
+      hidden 7168, gate+up N=4096, 65536 routed rows with per-expert counts drawn from a multinomial
+      over softmax(N(0,1) logits), seed 0; forward + dgrad + wgrad through ``grouped_gemm_fp8``:
+      activation quantise (1x128 row copy + segment-padded 128x1 column copy), weight quantise
+      (128x128 tiles, redone every forward as the reference does), forward GEMM, grad-out quantise,
+      dgrad GEMM, wgrad variable-K GEMM.
+  c5: the same op at the Qwen3-30B-A3B shape -- 128 experts, hidden 2048, gate+up N=1536, 32768 rows,
+      Zipf(1.2) counts with at least 8 empty groups.
+  c1: blockwise quantise + GEMM, A [256,1024] x B [512,1024]^T, forward (L2 flushed between steps).
+  c2: tensorwise dense GEMM, [8192,4096] x [14336,4096]^T, forward.
+  c3: rowwise dense GEMM forward + dgrad + wgrad, X [16384,8192], W [8192,8192].
+
+With N > 1 ranks (c4 / c5) the experts are sharded E/N per GPU, the rows start evenly split over the ranks
+and travel to their expert's owner and back (strong scaling).  ``--exchange peer`` (default) writes rows
+straight into the owners' IPC-mapped buffers with this library's copy kernel; ``--exchange nccl`` uses
+all-to-alls.  ``--placement balanced`` (default) assigns experts to ranks by greedy balancing of the
+router's expected load; ``contiguous`` keeps expert e on rank e // (E/N).
 
 Prints ONE JSON line on rank 0.  ``--impl reference`` times the CPU restatement of the reference's
 algorithm (oracle/, torch on the host cores) on a bounded sample of the same workload.
@@ -37,18 +45,48 @@ import torch
 REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO))
 
-E_TOTAL, HIDDEN, N_OUT, ROWS = 256, 7168, 4096, 65536
-WORKLOAD = "deepseek_v3_moe_gate_up_blockwise_fp8_grouped_gemm_fwd_dgrad_wgrad"
-METRIC = "blockwise_fp8_grouped_gemm_throughput"
+METRIC = {"c1": "blockwise_fp8_quantize_gemm_throughput", "c2": "tensorwise_fp8_gemm_throughput",
+          "c3": "rowwise_fp8_gemm_fwd_dgrad_wgrad_throughput", "c4": "blockwise_fp8_grouped_gemm_throughput",
+          "c5": "blockwise_fp8_grouped_gemm_throughput"}
 UNIT = "TFLOP/s"
+GROUPED = {
+    "c4": dict(E=256, K=7168, N=4096, ROWS=65536, counts="softmax",
+               workload="deepseek_v3_moe_gate_up_blockwise_fp8_grouped_gemm_fwd_dgrad_wgrad"),
+    "c5": dict(E=128, K=2048, N=1536, ROWS=32768, counts="zipf",
+               workload="qwen3_30b_a3b_moe_gate_up_blockwise_fp8_grouped_gemm_fwd_dgrad_wgrad"),
+}
+DENSE = {
+    "c1": dict(M=256, N=512, K=1024, gran="blockwise", bwd=False, w_scale=0.02,
+               workload="blockwise_fp8_quantize_gemm_256x512x1024_fwd"),
+    "c2": dict(M=8192, N=14336, K=4096, gran="tensorwise", bwd=False, w_scale=0.02,
+               workload="llama3_8b_mlp_up_tensorwise_fp8_gemm_fwd"),
+    "c3": dict(M=16384, N=8192, K=8192, gran="rowwise", bwd=True, w_scale=0.02,
+               workload="llama3_70b_attn_out_rowwise_fp8_gemm_fwd_dgrad_wgrad"),
+}
 
 
-def _counts(seed: int = 0) -> torch.Tensor:
+def _counts(cfg, seed: int = 0) -> torch.Tensor:
+    """Seeded per-expert row counts of the workload (the tests draw the same counts)."""
     g = torch.Generator().manual_seed(seed)
-    logits = torch.randn(E_TOTAL, generator=g)
-    p = torch.softmax(logits, 0)
-    idx = torch.multinomial(p, ROWS, replacement=True, generator=g)
-    return torch.bincount(idx, minlength=E_TOTAL).to(torch.int64)
+    E, rows = cfg["E"], cfg["ROWS"]
+    if cfg["counts"] == "softmax":
+        # multinomial over softmax(N(0,1) logits)
+        p = torch.softmax(torch.randn(E, generator=g), 0)
+        idx = torch.multinomial(p, rows, replacement=True, generator=g)
+        return torch.bincount(idx, minlength=E).to(torch.int64)
+    # Zipf(s = 1.2) over a seeded permutation of the experts; the 8 smallest groups are emptied into the largest
+    perm = torch.randperm(E, generator=g)
+    p = torch.arange(1, E + 1, dtype=torch.float64).pow(-1.2)
+    p = (p / p.sum()).to(torch.float32)
+    pe = torch.empty(E)
+    pe[perm] = p
+    idx = torch.multinomial(pe, rows, replacement=True, generator=g)
+    counts = torch.bincount(idx, minlength=E).to(torch.int64)
+    order = torch.argsort(counts, stable=True)
+    moved = counts[order[:8]].sum()
+    counts[order[:8]] = 0
+    counts[order[-1]] += moved
+    return counts
 
 
 def _peaks():
@@ -61,24 +99,29 @@ def _peaks():
 
 
 # ---------------------------------------------------------------------------------------------------
-# clocks sampled during the timed region
+# clocks sampled during the timed region (read-only nvidia-smi query of this rank's GPU, by UUID)
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, device_index: int):
+        self.rows, self.proc, self.err = [], None, ""
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            self.target = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:  # noqa: BLE001 - fall back to the index
+            self.target = str(device_index)
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20", "-i",
-                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 self.target], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except OSError as exc:
+            self.proc, self.err = None, repr(exc)
         return self
 
     def _read(self):
@@ -93,6 +136,10 @@ class ClockSampler:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+            try:
+                self.err = (self.proc.stderr.read() or "")[-300:]
+            except Exception:  # noqa: BLE001
+                pass
         return False
 
     def summary(self):
@@ -108,69 +155,129 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
+            if self.err:
+                print(f"[bench] nvidia-smi gave no clock samples: {self.err}", file=sys.stderr)
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # ---------------------------------------------------------------------------------------------------
-# CPU arm: the oracle (a port of the reference's algorithm) on a bounded sample
+# CPU arm: the oracle (a port of the reference's algorithm) on a bounded sample of each workload
 # ---------------------------------------------------------------------------------------------------
-def cpu_sample_step(sample):
-    """quantise -> dequantise -> fp32 matmul, forward + dgrad + wgrad, for the sample's experts."""
-    from oracle import fp8_oracle as O
-
-    a, w, gy, lens, offs = sample
-    E4 = torch.float8_e4m3fn
-    q_row, q_col, s_row, s_col, vk_lens, vk_offs, _, pu = O.quant_segment_row_col(a, E4, 128, lens, offs)
-    wq, w_s = O.quant_block2d(w, E4)
-    out = O.grouped_gemm_blockwise(q_row, s_row, wq, w_s, offs, True, torch.bfloat16)
-    g_row, g_col, gs_row, gs_col, _, _, _, _ = O.quant_segment_row_col(gy, E4, 128, lens, offs)
-    dx = O.grouped_gemm_blockwise(g_row, gs_row, wq, w_s, offs, False, torch.bfloat16)
-    dw = O.grouped_gemm_blockwise_variable_k(g_col[:pu], gs_col[: pu // 128], q_col[:pu], s_col[: pu // 128], vk_offs,
-                                             torch.bfloat16)
-    return out, dx, dw
+def _host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
-def make_cpu_sample(num_experts: int):
-    counts = _counts()
+def _cpu_grouped_sample(cfg, num_experts: int):
+    counts = _counts(cfg)
     g = torch.Generator().manual_seed(1)
-    # the experts whose row counts are nearest the mean (ROWS / E_TOTAL): a representative slice
-    pick = torch.argsort((counts - ROWS // E_TOTAL).abs(), stable=True)[:num_experts]
+    mean = cfg["ROWS"] // cfg["E"]
+    pick = torch.argsort((counts - mean).abs(), stable=True)[:num_experts]  # experts nearest the mean load
     lens = counts[pick].clone()
     offs = torch.zeros(num_experts + 1, dtype=torch.int64)
     offs[1:] = torch.cumsum(lens, 0)
     m = int(offs[-1])
-    a = torch.randn(m, HIDDEN, generator=g).to(torch.bfloat16)
-    w = (torch.randn(num_experts, N_OUT, HIDDEN, generator=g) * 0.02).to(torch.bfloat16)
-    gy = (torch.randn(m, N_OUT, generator=g) * 1e-3).to(torch.bfloat16)
-    return (a, w, gy, lens, offs), 3 * 2 * m * N_OUT * HIDDEN
+    a = torch.randn(m, cfg["K"], generator=g).to(torch.bfloat16)
+    w = (torch.randn(num_experts, cfg["N"], cfg["K"], generator=g) * 0.02).to(torch.bfloat16)
+    gy = (torch.randn(m, cfg["N"], generator=g) * 1e-3).to(torch.bfloat16)
+    flops = 3 * 2 * m * cfg["N"] * cfg["K"]
+    what = (f"the {num_experts} of {cfg['E']} experts with row counts nearest the mean, {m} routed rows "
+            f"({flops / 1e9:.1f} GFLOP per step), torch CPU fp32")
+
+    def step():
+        from oracle import fp8_oracle as O
+
+        E4 = torch.float8_e4m3fn
+        q_row, q_col, s_row, s_col, _, vk_offs, _, pu = O.quant_segment_row_col(a, E4, 128, lens, offs)
+        wq, w_s = O.quant_block2d(w, E4)
+        out = O.grouped_gemm_blockwise(q_row, s_row, wq, w_s, offs, True, torch.bfloat16)
+        g_row, g_col, gs_row, gs_col, _, _, _, _ = O.quant_segment_row_col(gy, E4, 128, lens, offs)
+        dx = O.grouped_gemm_blockwise(g_row, gs_row, wq, w_s, offs, False, torch.bfloat16)
+        dw = O.grouped_gemm_blockwise_variable_k(g_col[:pu], gs_col[: pu // 128], q_col[:pu], s_col[: pu // 128],
+                                                 vk_offs, torch.bfloat16)
+        return out, dx, dw
+
+    return step, flops, what
 
 
-def time_cpu(steps: int, warmup: int, num_experts: int):
-    sample, flops = make_cpu_sample(num_experts)
+def _cpu_dense_sample(cfg):
+    from oracle import fp8_oracle as O
+
+    E4 = torch.float8_e4m3fn
+    g = torch.Generator().manual_seed(0)
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    ms = min(M, 2048)  # bounded sample: the first `ms` rows of the activations (all of N and K)
+    x = torch.randn(ms, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * cfg["w_scale"]).to(torch.bfloat16)
+    gy = (torch.randn(ms, N, generator=g) * 1e-3).to(torch.bfloat16)
+    gemms = 3 if cfg["bwd"] else 1
+    flops = gemms * 2 * ms * N * K
+    what = (f"{ms} of {M} activation rows, all of N={N} and K={K}, {gemms} GEMM(s) "
+            f"({flops / 1e9:.1f} GFLOP per step), torch CPU fp32")
+
+    def step():
+        if cfg["gran"] == "blockwise":
+            aq, a_s, _, _ = O.quant_block1d_dual(x, E4)
+            bq, b_s = O.quant_block2d(w, E4)
+            return O.gemm_blockwise_nt(aq, a_s, bq, b_s, torch.bfloat16)
+        if cfg["gran"] == "tensorwise":
+            aq, a_s = O.quant_tensorwise(x, E4)
+            bq, b_s = O.quant_tensorwise(w, E4)
+            return O.gemm_tensorwise(aq, a_s, bq, b_s, False, True, torch.bfloat16)
+        # rowwise, with the backward operands re-quantised from the dequantised forward operands
+        aq, a_s = O.quant_rowwise(x, E4, -1)
+        bq, b_s = O.quant_rowwise(w, E4, -1)
+        out = O.gemm_rowwise(aq, a_s, bq, b_s, False, True, torch.bfloat16)
+        a_t_q, a_t_s = O.quant_rowwise(O.dequant_rowwise(aq, a_s, torch.bfloat16), E4, -2)
+        b_t_q, b_t_s = O.quant_rowwise(O.dequant_rowwise(bq, b_s, torch.bfloat16), E4, -2)
+        gq, g_s = O.quant_rowwise(gy, E4, -1)
+        gtq, gt_s = O.quant_rowwise(gy, E4, -2)
+        dx = O.gemm_rowwise(gq, g_s, b_t_q, b_t_s, False, False, torch.bfloat16)
+        dw = O.gemm_rowwise(gtq, gt_s, a_t_q, a_t_s, True, False, torch.bfloat16)
+        return out, dx, dw
+
+    return step, flops, what
+
+
+def time_cpu(config: str, steps: int, warmup: int):
+    """The oracle timed on the host cores with every thread this process may use."""
+    torch.set_num_threads(_host_threads())  # torchrun exports OMP_NUM_THREADS=1; the CPU arm runs on rank 0 alone
+    if config in GROUPED:
+        step, flops, what = _cpu_grouped_sample(GROUPED[config], num_experts=8)
+    else:
+        step, flops, what = _cpu_dense_sample(DENSE[config])
     for _ in range(warmup):
-        cpu_sample_step(sample)
+        step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu_sample_step(sample)
+        step()
     dt = (time.perf_counter() - t0) / max(steps, 1)
-    rows = int(sample[4][-1])
-    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"the {num_experts} of {E_TOTAL} experts with row counts nearest the mean, {rows} routed rows "
-                      f"({flops / 1e9:.1f} GFLOP per step), torch CPU fp32", "ms_per_step": dt * 1e3}
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": what,
+            "ms_per_step": dt * 1e3}
+
+
+def _workload_config(config: str, world: int = 1):
+    if config in GROUPED:
+        c = GROUPED[config]
+        return {"workload": c["workload"], "experts": c["E"], "hidden": c["K"], "n": c["N"], "routed_rows": c["ROWS"]}
+    c = DENSE[config]
+    return {"workload": c["workload"], "m": c["M"], "n": c["N"], "k": c["K"], "granularity": c["gran"]}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    r = time_cpu(args.steps, args.warmup, num_experts=4)
+    r = time_cpu(args.config, args.steps, args.warmup)
+    cfg = _workload_config(args.config)
+    cfg["sampled"] = True
     line = {
-        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC[args.config], "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 dequantise-then-matmul on CPU)",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "experts": E_TOTAL, "hidden": HIDDEN, "n": N_OUT,
-                                        "routed_rows": ROWS, "sampled": True},
+        "data": "synthetic", "config": cfg,
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -178,81 +285,242 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm: shared pieces
 # ---------------------------------------------------------------------------------------------------
-def _time_e2e(args, step, barrier, a, gy, rows_here, dev):
-    """The same step with activations / grad-out arriving from pinned host memory and the forward
-    output and activation gradient returned to it, all inside the timed region.  Copies run on their
-    own streams with double-buffered device inputs, so step i+1's upload and step i-1's download
-    overlap step i's kernels (every step still moves all of its own bytes)."""
-    a_host = torch.empty((rows_here, HIDDEN), dtype=torch.bfloat16).pin_memory()
-    gy_host = torch.empty((rows_here, N_OUT), dtype=torch.bfloat16).pin_memory()
-    a_host.copy_(a.detach())
-    gy_host.copy_(gy)
-    out_host = torch.empty((rows_here, N_OUT), dtype=torch.bfloat16).pin_memory()
-    ga_host = torch.empty((rows_here, HIDDEN), dtype=torch.bfloat16).pin_memory()
-    a_dev = [torch.empty((rows_here, HIDDEN), device=dev, dtype=torch.bfloat16) for _ in range(2)]
-    gy_dev = [torch.empty_like(gy) for _ in range(2)]
-    cur = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    in_ev = [torch.cuda.Event() for _ in range(2)]
-    free_ev = [torch.cuda.Event() for _ in range(2)]
-    for ev in free_ev:
-        ev.record(cur)
+class HostPipe:
+    """Host-buffer pass: every step copies its inputs from pinned host memory and its results back to
+    it inside the timed region.  Copies run on their own streams with double-buffered device inputs,
+    so step i+1's upload and step i-1's download overlap step i's kernels (every step still moves all
+    of its own bytes)."""
 
-    def e2e_step(i):
+    def __init__(self, dev, inputs, step, compute: bool = True):
+        self.dev, self.step, self.compute = dev, step, compute
+        self.host_in = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in inputs]
+        for h, t in zip(self.host_in, inputs):
+            h.copy_(t.detach())
+        self.dev_in = [[torch.empty_like(t.detach()) for t in inputs] for _ in range(2)]
+        self.host_out = None
+        self.cur = torch.cuda.current_stream()
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.in_ev = [torch.cuda.Event() for _ in range(2)]
+        self.free_ev = [torch.cuda.Event() for _ in range(2)]
+        for ev in self.free_ev:
+            ev.record(self.cur)
+        self.h2d = sum(t.numel() * t.element_size() for t in inputs)
+        self.d2h = 0
+
+    def run(self, i):
         b = i % 2
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(free_ev[b])  # the step that last read this buffer has finished with it
-            a_dev[b].copy_(a_host, non_blocking=True)
-            gy_dev[b].copy_(gy_host, non_blocking=True)
-            in_ev[b].record(s_in)
-        cur.wait_event(in_ev[b])
-        out, ga, _ = step(a_dev[b].detach().requires_grad_(True), gy_dev[b])
-        free_ev[b].record(cur)
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(self.free_ev[b])  # the step that last read this buffer has finished with it
+            for d, h in zip(self.dev_in[b], self.host_in):
+                d.copy_(h, non_blocking=True)
+            self.in_ev[b].record(self.s_in)
+        self.cur.wait_event(self.in_ev[b])
+        outs = self.step(*self.dev_in[b]) if self.compute else self._echo(b)
+        self.free_ev[b].record(self.cur)
+        if self.host_out is None:
+            self.host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+            self.d2h = sum(o.numel() * o.element_size() for o in outs)
         done = torch.cuda.Event()
-        done.record(cur)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
-            out_host.copy_(out.detach(), non_blocking=True)
-            ga_host.copy_(ga, non_blocking=True)
-        out.record_stream(s_out)
-        ga.record_stream(s_out)
+        done.record(self.cur)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(done)
+            for h, o in zip(self.host_out, outs):
+                h.copy_(o.detach(), non_blocking=True)
+        for o in outs:
+            o.record_stream(self.s_out)
 
-    for i in range(2):
-        e2e_step(i)
-    cur.wait_stream(s_out)
+    def _echo(self, b):
+        # copy-only ceiling: results of the recorded shapes, nothing computed
+        return self._like
+
+    def time(self, steps, barrier):
+        for i in range(2):
+            self.run(i)
+        self.cur.wait_stream(self.s_out)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            self.run(i)
+        self.cur.wait_stream(self.s_in)
+        self.cur.wait_stream(self.s_out)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
+
+def time_e2e(dev, inputs, step, steps, barrier):
+    """(ms per step with compute, ms per step copies only, h2d bytes, d2h bytes)"""
+    pipe = HostPipe(dev, inputs, step)
+    ms = pipe.time(steps, barrier)
+    ceil = HostPipe(dev, inputs, step, compute=False)
+    ceil.host_out = pipe.host_out
+    ceil.d2h = pipe.d2h
+    ceil._like = [torch.empty(h.shape, dtype=h.dtype, device=dev) for h in pipe.host_out]
+    ms_copy = ceil.time(steps, barrier)
+    return ms, ms_copy, pipe.h2d, pipe.d2h
+
+
+def _roof(name, kernel, flops, nbytes, times_ms, peaks, fp8_peak, traffic=None):
+    """Roofline record of one kernel: the bound is whichever floor (tensor or HBM) is the longer one."""
+    if not times_ms:
+        return None
+    t = statistics.mean(times_ms) * 1e-3
+    t_tensor = flops / (fp8_peak * 1e12) if flops else 0.0
+    t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9)
+    rec = {"entry_point": name, "kernel": kernel, "avg_launch_ms": t * 1e3, "launches": len(times_ms),
+           "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tensor_floor_ms": t_tensor * 1e3,
+           "hbm_floor_ms": t_hbm * 1e3, "traffic": traffic}
+    if t_tensor >= t_hbm:
+        ach = flops / t / 1e12
+        rec.update({"bound": "tensor", "achieved": ach, "peak": fp8_peak, "unit": "TFLOP/s", "frac": ach / fp8_peak,
+                    "peak_source": f"2 x sustained bf16 cuBLAS rate of MEASURED_PEAKS.json ({peaks['source']})"})
+    else:
+        ach = nbytes / t / 1e9
+        rec.update({"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": ach / peaks["hbm_gbs"],
+                    "peak_source": f"copy bandwidth of MEASURED_PEAKS.json ({peaks['source']})"})
+    return rec
+
+
+def _finish_line(args, line, kernel_ms, roofs, clocks, launches, status):
+    roofs = [r for r in roofs if r]
+    # the kernel with the largest share of the step leads; the peer copy (an NVLink-bound kernel) never does
+    roofs.sort(key=lambda r: (r["bound"] not in ("hbm", "tensor"), -r["avg_launch_ms"] * r["launches"]))
+    line.update({
+        "gpu_launches": launches,
+        "kernel_ms": {k: {"launches": len(v), "avg_ms": statistics.mean(v), "total_ms": sum(v)} for k, v in kernel_ms.items()},
+        "gemm_status": status, "clocks": clocks,
+        "roofline": roofs[0] if roofs else None, "roofline_other_kernels": roofs[1:],
+    })
+    if line["n_gpus"] == 1 and not args.no_cpu_baseline:
+        r = time_cpu(args.config, steps=3, warmup=1)
+        line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+
+
+def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None):
+    """(ms per step, per-entry-point kernel times, clock summary, launches)"""
+    from primus_turbo_b200 import _lib
+
+    for _ in range(max(warmup, 3)):
+        step(*inputs)
     barrier()
-    e2e_steps = max(2, min(args.steps, 10))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    cur.wait_stream(s_in)
-    cur.wait_stream(s_out)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    h2d = a_host.numel() * 2 + gy_host.numel() * 2
-    d2h = out_host.numel() * 2 + ga_host.numel() * 2
-    return e2e_ms, h2d, d2h
+    launches0 = _lib.launch_count
+    with ClockSampler(device_index) as clocks, _lib.record_kernel_times() as rec:
+        barrier()
+        if flush is None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for _ in range(steps):
+                step(*inputs)
+            ev1.record()
+            barrier()
+            ms = ev0.elapsed_time(ev1) / steps
+        else:
+            evs = []
+            for _ in range(steps):
+                flush.zero_()  # evict the inputs from L2 between timed iterations (not timed)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step(*inputs)
+                e1.record()
+                evs.append((e0, e1))
+            barrier()
+            ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+    return ms, rec.durations_ms(), clocks.summary(), _lib.launch_count - launches0
 
 
+# ---------------------------------------------------------------------------------------------------
+# dense configurations (c1, c2, c3): one GPU
+# ---------------------------------------------------------------------------------------------------
+def run_dense(args):
+    from primus_turbo_b200 import _lib
+    from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity
+    from primus_turbo_b200.pytorch.ops import gemm_fp8
+
+    assert args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1, "the dense configurations run on one GPU"
+    cfg = DENSE[args.config]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    gran = {"blockwise": ScalingGranularity.BLOCKWISE, "tensorwise": ScalingGranularity.TENSORWISE,
+            "rowwise": ScalingGranularity.ROWWISE}[cfg["gran"]]
+    qcfg = Float8QuantConfig(granularity=gran, block_size=128 if cfg["gran"] == "blockwise" else None)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    w = (torch.randn(N, K, generator=g) * cfg["w_scale"]).to(torch.bfloat16).to(dev).requires_grad_(cfg["bwd"])
+    gy = (torch.randn(M, N, generator=g) * 1e-3).to(torch.bfloat16).to(dev)
+    gemms = 3 if cfg["bwd"] else 1
+    flops = gemms * 2 * M * N * K
+
+    def step(x_in, gy_in=None):
+        if not cfg["bwd"]:
+            return (gemm_fp8(x_in, w, trans_b=True, config=qcfg),)
+        x_in = x_in.detach().requires_grad_(True)
+        out = gemm_fp8(x_in, w, trans_b=True, config=qcfg)
+        gx, gw = torch.autograd.grad(out, (x_in, w), gy_in)
+        return out, gx, gw
+
+    def barrier():
+        torch.cuda.synchronize()
+
+    inputs = (x, gy) if cfg["bwd"] else (x,)
+    in_bytes = (M * K + N * K) * 2
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if in_bytes < (200 << 20) else None
+    ms, kernel_ms, clocks, launches = _timed(step, inputs, args.steps, args.warmup, barrier, 0, flush)
+    status = _lib.gemm_status()
+    e2e = None
+    if not args.no_e2e:
+        # inputs from the host: the activations (and grad-out); results back: out (c3: also grad_x; the weight
+        # and its gradient stay resident)
+        def e2e_step(*ins):
+            return step(*ins)[:2]
+
+        e2e_ms, copy_ms, h2d, d2h = time_e2e(dev, inputs, e2e_step, max(2, min(args.steps, 10)), barrier)
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "copy_only_ms_per_step": copy_ms,
+               "note": "activations (and grad-out) from pinned host memory, out (and grad-activation) back to it; "
+                       "copy_only_ms_per_step is the same traffic with no kernels in between (the PCIe ceiling)"}
+    peaks = _peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    gemm_t = kernel_ms.get("ptb_gemm_fp8", [])
+    per_gemm = 2 * M * N * K
+    op_bytes = M * K + N * K + M * N * 2  # fp8 operands in, bf16 out (forward shape; dgrad / wgrad permute M, N, K)
+    roofs = [_roof("ptb_gemm_fp8", f"fp8_gemm_kernel<{cfg['gran']}, bf16> (dense, {gemms} launch(es) per step)", per_gemm,
+                   op_bytes, gemm_t, peaks, fp8_peak)]
+    for name, v in kernel_ms.items():
+        if name.startswith("ptb_quant") and v:
+            n_el = {"ptb_quant_fp8_block2d": N * K}.get(name, M * max(K, N) if cfg["bwd"] else M * K)
+            roofs.append(_roof(name, "quantise kernel(s) of this entry point (bytes of the largest operand it sees)", 0,
+                               n_el * 3.03, v, peaks, fp8_peak))
+    value = flops / (ms * 1e-3) / 1e12
+    wl = _workload_config(args.config)
+    wl["l2"] = ("L2 flushed (256 MiB memset) between timed iterations" if flush is not None
+                else "inputs larger than L2")
+    line = {"metric": METRIC[args.config], "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 operands, fp32 accumulate, bf16 in/out", "data": "synthetic",
+            "config": wl, "per_gpu_tflops": value, "pct_of_fp8_peak_per_gpu": 100.0 * value / fp8_peak,
+            "fp8_peak_tflops": fp8_peak, "e2e": e2e}
+    _finish_line(args, line, kernel_ms, roofs, clocks, launches, status)
+
+
+# ---------------------------------------------------------------------------------------------------
+# grouped configurations (c4, c5): 1..8 GPUs
+# ---------------------------------------------------------------------------------------------------
 def _bind_host_threads_near_gpu(index: int) -> None:
-    """Pin this process to the CPU cores NVML reports as local to its GPU, so that the pinned host
-    buffers of the host-buffer pass are first-touched on that GPU's NUMA node (with several ranks
-    on one box the default placement funnels every rank's PCIe traffic through one node).  Only
-    reads device properties; any failure leaves the affinity as it was."""
+    """Pin this process to the CPU cores NVML reports as local to its GPU (read-only query; any failure
+    leaves the affinity as it was)."""
     try:
         import pynvml
 
         pynvml.nvmlInit()
         props = torch.cuda.get_device_properties(index)
-        if hasattr(props, "pci_bus_id") and hasattr(props, "pci_domain_id"):  # robust to device remapping
-            bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
-            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
-        else:
-            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
         words = (os.cpu_count() + 63) // 64
         mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
         cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
@@ -263,216 +531,309 @@ def _bind_host_threads_near_gpu(index: int) -> None:
         pass
 
 
-def run_ours(args):
+def _ep_parity(dist, rank, world, dev, cfg, qcfg, order_pos_counts, x, gy, w, ep_step, sample_positions):
+    """Before timing: for a few sampled experts, every rank recomputes -- on one GPU, with the single-GPU
+    op -- the rows it routes to that expert (the owner broadcasts the expert's weight) and compares with
+    what the expert-parallel step returned for those rows: out and grad_a must match bit for bit."""
+    from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
+
+    e_loc = cfg["E"] // world
+    out, ga, _ = ep_step(x.detach().requires_grad_(True), gy)
+    ok = True
+    offs = torch.cumsum(order_pos_counts, 0) - order_pos_counts
+    for p in sample_positions:
+        owner = p // e_loc
+        wp = w[p - owner * e_loc].detach().clone() if rank == owner else torch.empty(
+            (cfg["N"], cfg["K"]), dtype=torch.bfloat16, device=dev)
+        dist.broadcast(wp, src=owner)
+        n, lo = int(order_pos_counts[p]), int(offs[p])
+        if n == 0:
+            continue
+        xs = x[lo : lo + n].detach().requires_grad_(True)
+        lens = torch.tensor([n], dtype=torch.int64, device=dev)
+        o1 = grouped_gemm_fp8(xs, wp.unsqueeze(0), lens, config=qcfg)
+        (g1,) = torch.autograd.grad(o1, xs, gy[lo : lo + n])
+        ok = ok and torch.equal(o1, out[lo : lo + n]) and torch.equal(g1, ga[lo : lo + n])
+    flag = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
+def run_grouped(args):
     import torch.distributed as dist
 
     from primus_turbo_b200 import _lib
     from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity
-    from primus_turbo_b200.pytorch.dist.expert_parallel import (
-        build_exchange_plan, ep_grouped_gemm_fp8, expert_parallel_apply)
+    from primus_turbo_b200.pytorch.core.quantized_tensor import create_quantized_weight
+    from primus_turbo_b200.pytorch.dist import expert_parallel as EP
     from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in the product")
+    cfg = dict(GROUPED[args.config])
+    if args.experts:
+        cfg["E"] = args.experts
+    if args.rows:
+        cfg["ROWS"] = args.rows
+    E, K, N, ROWS = cfg["E"], cfg["K"], cfg["N"], cfg["ROWS"]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    assert E % world == 0 and ROWS % world == 0
     if world > 1 and args.bind_cpus:
         _bind_host_threads_near_gpu(local_rank)
+    host_group = board = exchange = None
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
-        if args.ep_overlap:
-            # the collective that runs beside wgrad must fit on the SMs wgrad leaves free
-            os.environ.setdefault("NCCL_MAX_CTAS", str(args.ep_reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
         host_group = dist.new_group(backend="gloo")  # CPU group: set-up traffic and the fallback count gather
-        if args.plan == "host":
-            # ranks of one machine exchange their routing counts through a shared-memory board
-            # (a gloo gather costs 2-4 ms per step at eight ranks and made the step host-bound)
-            try:
-                from primus_turbo_b200.pytorch.dist.expert_parallel import SharedCountsBoard
+        try:
+            board = EP.SharedCountsBoard(E, group=host_group)  # ranks of one machine: counts through shared memory
+        except Exception as exc:  # noqa: BLE001 - keep the gloo group
+            print(f"[bench] shared counts board unavailable ({exc!r}); using gloo", file=sys.stderr)
+    qcfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
+    e_loc = E // world
 
-                host_group = SharedCountsBoard(E_TOTAL, group=host_group)
-            except Exception as exc:  # noqa: BLE001 - keep the gloo group
-                print(f"[bench] shared counts board unavailable ({exc!r}); using gloo", file=sys.stderr)
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    assert E_TOTAL % world == 0 and ROWS % world == 0
-    cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
-    e_loc = E_TOTAL // world
-
-    # ---- synthetic inputs (seeded, generated on the device that holds them) -----------------------
-    counts = _counts()
+    # ---- routing: global counts, expert placement, this rank's rows ---------------------------------------
+    counts = _counts(cfg)
+    imbalance_contiguous = EP.load_imbalance(counts, world)
+    if world > 1 and args.placement == "balanced":
+        # the router's expected load is the distribution the counts were drawn from; the realised counts
+        # of the seeded draw stand in for it
+        order = EP.balanced_expert_order(counts, world)
+    else:
+        order = torch.arange(E)
+    pos_counts = counts[order]  # rows per placement position (rank r owns positions [r*e_loc, (r+1)*e_loc))
+    imbalance = EP.load_imbalance(pos_counts, world)
     torch.manual_seed(1234 + rank)
     rows_here = ROWS // world
     if world == 1:
-        counts_here = counts
+        counts_here = pos_counts
     else:
         # every source rank holds ROWS/world rows whose experts are drawn i.i.d. from the same routing
         g = torch.Generator().manual_seed(100 + rank)
-        idx = torch.multinomial(counts.double() / counts.sum(), rows_here, replacement=True, generator=g)
-        counts_here = torch.bincount(idx, minlength=E_TOTAL).to(torch.int64)
+        idx = torch.multinomial(pos_counts.double() / pos_counts.sum(), rows_here, replacement=True, generator=g)
+        counts_here = torch.bincount(idx, minlength=E).to(torch.int64)
     counts_dev = counts_here.to(dev)
-    a = torch.randn(rows_here, HIDDEN, device=dev, dtype=torch.bfloat16).requires_grad_(True)
-    w = (torch.randn(e_loc, N_OUT, HIDDEN, device=dev, dtype=torch.bfloat16) * 0.02).requires_grad_(True)
-    gy = torch.randn(rows_here, N_OUT, device=dev, dtype=torch.bfloat16) * 1e-3
-    flops_step = 3 * 2 * ROWS * N_OUT * HIDDEN  # whole job
+    a = torch.randn(rows_here, K, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(e_loc, N, K, device=dev, dtype=torch.bfloat16) * 0.02).requires_grad_(True)
+    gy = torch.randn(rows_here, N, device=dev, dtype=torch.bfloat16) * 1e-3
+    flops_step = 3 * 2 * ROWS * N * K  # whole job
+    plan_ms = []
 
-    def step(a_in, gy_in):
-        if world == 1:
-            out = grouped_gemm_fp8(a_in, w, counts_dev, config=cfg)
-        else:
-            # the synthetic router's counts live on the host, so the exchange plan (rebuilt every
-            # step, as routing changes every step in training) never waits on the device stream
-            if args.plan == "host":
-                plan = build_exchange_plan(counts_dev, counts_host=counts_here, host_group=host_group)
+    if world > 1 and args.exchange == "peer":
+        from primus_turbo_b200.pytorch.dist.peer_exchange import PeerExchange
+
+        cap = int(max(2 * ROWS // world, ROWS // world + 4096))
+        exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas)
+    state = {"exchange": exchange}
+
+    def make_step(weight):
+        def local_fn(rows, lens):
+            return grouped_gemm_fp8(rows, weight, lens, config=qcfg)
+
+        def step(a_in, gy_in):
+            a_in = a_in if a_in.requires_grad else a_in.detach().requires_grad_(True)
+            if world == 1:
+                out = grouped_gemm_fp8(a_in, weight, counts_dev, config=qcfg)
             else:
-                plan = build_exchange_plan(counts_dev)
-            if args.ep_overlap:
-                # weight quantisation beside the dispatch, wgrad beside the return of grad_a
-                out = ep_grouped_gemm_fp8(a_in, w, counts_dev, config=cfg, plan=plan, overlap=True,
-                                          reserve_sms=args.ep_reserve_sms)
-            else:
-                out = expert_parallel_apply(
-                    a_in, counts_dev, lambda rows, lens: grouped_gemm_fp8(rows, w, lens, config=cfg), plan=plan)
-        ga, gw = torch.autograd.grad(out, (a_in, w), gy_in)
-        return out, ga, gw
+                # the synthetic router's counts live on the host, so the exchange plan (rebuilt every step, as
+                # routing changes every step in training) never waits on the device stream
+                t0 = time.perf_counter()
+                if state["exchange"] is not None:
+                    plan = EP.build_peer_plan(counts_here, board or host_group, dev)
+                    plan_ms.append((time.perf_counter() - t0) * 1e3)
+                    out = EP.expert_parallel_apply_peer(a_in, local_fn, state["exchange"], plan)
+                else:
+                    plan = EP.build_exchange_plan(counts_dev, counts_host=counts_here, host_group=board or host_group)
+                    plan_ms.append((time.perf_counter() - t0) * 1e3)
+                    out = EP.expert_parallel_apply(a_in, counts_dev, local_fn, plan=plan)
+            leaf = weight
+            ga, gw = torch.autograd.grad(out, (a_in, leaf), gy_in)
+            return out, ga, gw
+
+        return step
+
+    step = make_step(w)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing ---------------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        step(a, gy)
-    barrier()
-    launches0 = _lib.launch_count
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks, _lib.record_kernel_times() as rec:
-        barrier()
-        ev0.record()
-        for _ in range(args.steps):
+    ep_parity = None
+    if world > 1 and exchange is not None:
+        # one guarded step: if the peer mapping cannot be set up on this machine, every rank falls back to
+        # the all-to-all exchange (still this library's kernels on every GPU; nothing runs on the host)
+        try:
             step(a, gy)
-        ev1.record()
-        barrier()
-    ms = ev0.elapsed_time(ev1) / args.steps
-    launches = _lib.launch_count - launches0
-    kernel_ms = rec.durations_ms()
-    status = _lib.gemm_status()
-
-    # ---- end to end: host buffers in, host buffers out -----------------------------------------------
-    e2e_ms, h2d, d2h = float("nan"), 0, 0
-    if not args.no_e2e:
-        e2e_ms, h2d, d2h = _time_e2e(args, step, barrier, a, gy, rows_here, dev)
-
-    # ---- max over ranks ---------------------------------------------------------------------------------
+            torch.cuda.synchronize()
+            ok = 1
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] rank {rank}: peer exchange unavailable ({exc!r}); falling back to NCCL all-to-alls",
+                  file=sys.stderr)
+            ok = 0
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            state["exchange"], args.exchange = None, "nccl"
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        nz = torch.nonzero(pos_counts > 0).flatten().tolist()
+        sample = sorted({nz[0], nz[len(nz) // 3], nz[(2 * len(nz)) // 3], nz[-1]})
+        ep_parity = _ep_parity(dist, rank, world, dev, cfg, qcfg, counts_here, a, gy, w, step, sample)
+
+    # ---- device-resident timing ---------------------------------------------------------------------------
+    plan_ms.clear()
+    ms, kernel_ms, clocks, launches = _timed(step, (a, gy), args.steps, args.warmup, barrier, local_rank)
+    plan_host_ms = statistics.mean(plan_ms[-args.steps:]) if plan_ms else 0.0
+    status = _lib.gemm_status()
+    copy_status = _lib.copy_segments_status() if state["exchange"] is not None else 0
+
+    # ---- the same step with the weight quantised ahead of time (where the caller's weights allow it) ----
+    ms_cached = None
+    if not args.no_cached:
+        with torch.no_grad():
+            qw, _ = create_quantized_weight(w.detach().clone().requires_grad_(True), torch.float8_e4m3fn, qcfg)
+        step_cached = make_step(qw)
+        ms_cached, _, _, _ = _timed(step_cached, (a, gy), max(2, min(args.steps, 5)), 3, barrier, local_rank)
+
+    # ---- end to end: host buffers in, host buffers out --------------------------------------------------------
+    e2e_ms = copy_ms = float("nan")
+    h2d = d2h = 0
+    if not args.no_e2e:
+        def e2e_step(a_in, gy_in):
+            return step(a_in, gy_in)[:2]
+
+        e2e_ms, copy_ms, h2d, d2h = time_e2e(dev, (a, gy), e2e_step, max(2, min(args.steps, 10)), barrier)
+
+    # ---- max over ranks -------------------------------------------------------------------------------------------
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, ms_cached or 0.0, copy_ms, plan_host_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        ms, e2e_ms, copy_ms, plan_host_ms = float(t[0]), float(t[1]), float(t[3]), float(t[4])
+        ms_cached = float(t[2]) if ms_cached is not None else None
 
     if rank == 0:
         peaks = _peaks()
         fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]  # dense FP8 runs at twice the bf16 rate
         value = flops_step / (ms * 1e-3) / 1e12
-        # Rooflines.  The launch with the largest share of the step is the wgrad instance of
-        # fp8_gemm_kernel (variable-K, 2-3 contraction blocks per tile here): it must write the whole
-        # bf16 weight gradient, so its roof is HBM.  The forward / dgrad instance streams the FP8
-        # weights once and sits between the tensor and the HBM roof; both are reported.
-        # `traffic` is dram__bytes_read + dram__bytes_write per launch from the ncu capture of the
-        # 32-expert / 8192-row case (profiles/fp8_gemm_kernel_grouped_blockwise_32experts.md), scaled by
-        # experts x rows (traffic is proportional to both).
-        unit_factor = (E_TOTAL / world) / 32.0  # experts (and, with them, rows) per launch vs the captured case
-        fwd_dgrad = kernel_ms.get("ptb_grouped_gemm_fp8", [])
-        wgrad = kernel_ms.get("ptb_grouped_gemm_fp8_variable_k", [])
-        wq = kernel_ms.get("ptb_quant_fp8_block2d", [])
-        per_gemm_flops = 2 * ROWS * N_OUT * HIDDEN / world
-        pad_rows = ROWS / world * 1.244  # segment padding of the column copies (measured on this routing)
-        roof, others = None, []
-        if wgrad:
-            t_avg = statistics.mean(wgrad) * 1e-3
-            alg_bytes = e_loc * N_OUT * HIDDEN * 2 + pad_rows * (N_OUT + HIDDEN) * (1 + 4.0 / 128)
-            achieved = alg_bytes / t_avg / 1e9
-            roof = {"kernel": "fp8_gemm_kernel<block 1Dx1D, bf16> (grouped wgrad launch)", "bound": "hbm",
-                    "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "peak_source": f"copy bandwidth of MEASURED_PEAKS.json ({peaks['source']})",
-                    "traffic": 1.945e9 * unit_factor, "algorithmic_bytes": alg_bytes, "avg_launch_ms": t_avg * 1e3,
-                    "tflops": per_gemm_flops / t_avg / 1e12}
-        if fwd_dgrad:
-            t_avg = statistics.mean(fwd_dgrad) * 1e-3
-            achieved = per_gemm_flops / t_avg / 1e12
-            others.append({"kernel": "fp8_gemm_kernel<block 1x128 x 128x128, bf16> (grouped forward and dgrad launches)",
-                           "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                           "frac": achieved / fp8_peak,
-                           "peak_source": f"2 x sustained bf16 cuBLAS rate of MEASURED_PEAKS.json ({peaks['source']})",
-                           "traffic": 1.230e9 * unit_factor, "avg_launch_ms": t_avg * 1e3,
-                           "hbm_floor_ms": (e_loc * N_OUT * HIDDEN + (ROWS // world) * (HIDDEN + 2 * N_OUT)) /
-                                           (peaks["hbm_gbs"] * 1e9) * 1e3})
-        if wq:
-            t_avg = statistics.mean(wq) * 1e-3
-            alg_bytes = e_loc * N_OUT * HIDDEN * (3 + 4.0 / 16384)
-            achieved = alg_bytes / t_avg / 1e9
-            others.append({"kernel": "quant_block_kernel<128x128> (weight quantise)", "bound": "hbm", "achieved": achieved,
-                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                           "traffic": 2.790e9 * unit_factor, "avg_launch_ms": t_avg * 1e3})
-        kernels = {k: {"launches": len(v), "avg_ms": statistics.mean(v), "total_ms": sum(v)} for k, v in kernel_ms.items()}
+        # what rank 0's launches process (at N > 1: rank 0's share after the dispatch)
+        if world == 1:
+            lens0 = pos_counts
+        else:
+            lens0 = pos_counts.new_zeros(e_loc)
+            for r in range(world):
+                g = torch.Generator().manual_seed(100 + r)
+                idx = torch.multinomial(pos_counts.double() / pos_counts.sum(), rows_here, replacement=True, generator=g)
+                lens0 += torch.bincount(idx, minlength=E)[:e_loc]
+        rows0 = int(lens0.sum())
+        pad0 = int((((lens0 + 127) // 128) * 128).sum())  # rows of the segment-padded column copies
+        tile_rows0 = pad0  # rows the 128-row forward / dgrad tiles cover
+        gemm_flops = 2 * rows0 * N * K
+        # ncu dram__bytes_read + dram__bytes_write per launch on the captured 32-expert / 8192-row case of c4,
+        # over the algorithmic bytes of that case: scaled to this launch by its algorithmic bytes
+        traffic_ratio = {"wgrad": 1.945e9 / 1.997e9, "fwd": 1.230e9 / 1.062e9, "wq": 2.790e9 / 2.819e9} \
+            if args.config == "c4" else {}
+        b_wgrad = e_loc * N * K * 2 + pad0 * (N + K) * (1 + 4.0 / 128)
+        b_fwd = e_loc * N * K + rows0 * (K + 2 * N)
+        b_dgrad = e_loc * N * K + rows0 * (N + 2 * K)
+        b_wq = e_loc * N * K * (3 + 4.0 / 16384)
+        b_seg = lambda width: rows0 * width * (2 + 1 + 4.0 / 128) + pad0 * width * (1 + 4.0 / 128)  # noqa: E731
+        tr = lambda k, b: (traffic_ratio[k] * b if k in traffic_ratio else None)  # noqa: E731
+        roofs = [
+            _roof("ptb_grouped_gemm_fp8_variable_k", "fp8_gemm_kernel<block 1Dx1D, bf16> (grouped wgrad launch)", gemm_flops,
+                  b_wgrad, kernel_ms.get("ptb_grouped_gemm_fp8_variable_k", []), peaks, fp8_peak, tr("wgrad", b_wgrad)),
+            _roof("ptb_grouped_gemm_fp8", "fp8_gemm_kernel<block 1x128 x 128x128, bf16> (grouped forward and dgrad launches)",
+                  gemm_flops, (b_fwd + b_dgrad) / 2, kernel_ms.get("ptb_grouped_gemm_fp8", []), peaks, fp8_peak,
+                  tr("fwd", (b_fwd + b_dgrad) / 2)),
+            _roof("ptb_quant_fp8_block2d", "quant_block_kernel<128x128> (weight quantise)", 0, b_wq,
+                  kernel_ms.get("ptb_quant_fp8_block2d", []), peaks, fp8_peak, tr("wq", b_wq)),
+            _roof("ptb_quant_fp8_segment_row_col", "quant_block_kernel<row + padded column copy> (activation and grad-out)", 0,
+                  (b_seg(K) + b_seg(N)) / 2, kernel_ms.get("ptb_quant_fp8_segment_row_col", []), peaks, fp8_peak),
+        ]
+        if "ptb_copy_segments" in kernel_ms:
+            sent = rows_here * (K + N) * 2 * 2 / 4  # mean bytes per launch over the step's four exchanges
+            r = _roof("ptb_copy_segments", "copy_segments_kernel (dispatch / combine over peer memory)", 0, sent,
+                      kernel_ms["ptb_copy_segments"], peaks, fp8_peak)
+            r.update({"bound": "nvlink", "peak": 770.0, "peak_source": "measured peer copy, GB/s per direction",
+                      "achieved": sent * (world - 1) / world / (r["avg_launch_ms"] * 1e-3) / 1e9})
+            r["frac"] = r["achieved"] / r["peak"]
+            roofs.append(r)
+        step_kernels = sum(sum(v) for v in kernel_ms.values()) / args.steps
+        copy_k = sum(kernel_ms.get("ptb_copy_segments", [])) / args.steps
+        wl = _workload_config(args.config)
+        wl.update({"experts": E, "routed_rows": ROWS, "experts_per_gpu": e_loc, "parallelism": f"ep{world}",
+                   "exchange": (args.exchange if world > 1 else None), "placement": (args.placement if world > 1 else None),
+                   "load_imbalance_max_over_mean_rows": imbalance,
+                   "load_imbalance_contiguous_placement": imbalance_contiguous,
+                   "tile_padding_rows_over_rows": pad0 / max(rows0, 1),
+                   "l2": f"inputs larger than L2 ({e_loc * N * K / 1e9:.2f} GB of FP8 weights per pass)"})
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC[args.config], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 operands, fp32 accumulate, bf16 in/out", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "experts": E_TOTAL, "experts_per_gpu": e_loc, "hidden": HIDDEN,
-                       "n": N_OUT, "routed_rows": ROWS, "parallelism": f"ep{world}",
-                       "ep_overlap": bool(args.ep_overlap) if world > 1 else None,
-                       "load_imbalance_max_over_mean_rows": float(
-                           counts.view(world, -1).sum(1).max().item() * world / counts.sum().item()),
-                       "l2": "inputs larger than L2 (7.5 GB of FP8 weights per pass)"},
-            "per_gpu_tflops": value / world, "pct_of_fp8_peak_per_gpu": 100.0 * value / world / fp8_peak,
+            "config": wl, "per_gpu_tflops": value / world, "pct_of_fp8_peak_per_gpu": 100.0 * value / world / fp8_peak,
             "fp8_peak_tflops": fp8_peak,
+            "value_cached_weights": (flops_step / (ms_cached * 1e-3) / 1e12) if ms_cached else None,
+            "ms_per_step_cached_weights": ms_cached,
             "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "copy_only_ms_per_step": copy_ms,
                     "note": "activations and grad-out from pinned host memory, out and grad-activation back to it "
                             "(copy streams overlap the neighbouring steps' kernels); weights and their gradient stay "
-                            "resident"},
-            "gpu_launches": launches, "kernel_ms": kernels, "gemm_status": status,
-            "clocks": clocks.summary(), "roofline": roof, "roofline_other_kernels": others,
+                            "resident; copy_only_ms_per_step is the same traffic with no kernels in between"},
         }
-        if world == 1 and not args.no_cpu_baseline:
-            r = time_cpu(steps=5, warmup=1, num_experts=4)
-            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
+        if world > 1:
+            line["ep_parity"] = ep_parity
+            line["phases_ms"] = {"plan_host": plan_host_ms, "exchange_copy_kernels": copy_k,
+                                 "local_kernels": step_kernels - copy_k, "step": ms,
+                                 "not_in_kernels": ms - step_kernels,
+                                 "note": "rank 0's kernels; plan_host is host time that overlaps the device queue; "
+                                         "not_in_kernels covers the ordering collectives (or all-to-alls), "
+                                         "torch's copies and waiting for the slowest rank"}
+            line["copy_segments_status"] = copy_status
+        _finish_line(args, line, kernel_ms, roofs, clocks, launches, status)
     if world > 1:
+        if exchange is not None:
+            dist.barrier()
+            exchange.close()
+            dist.barrier()
+        if board is not None:
+            board.close()
         dist.destroy_process_group()
 
 
 def main():
-    global E_TOTAL, ROWS
     ap = argparse.ArgumentParser()
+    ap.add_argument("--config", choices=sorted(METRIC), default="c4")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--ep-overlap", type=int, default=0,
-                    help="N > 1: 1 = weight quantise beside the dispatch and wgrad beside the grad_a return "
-                         "(measured slower: both sides of each pair are HBM-bound); 0 = serial")
-    ap.add_argument("--plan", choices=["host", "device"], default="host",
-                    help="N > 1: where the exchange plan is computed (host: gloo gather + one pinned copy; "
-                         "device: NCCL gather + one host read of the split sizes)")
+    ap.add_argument("--no-cached", action="store_true", help="skip the pass with weights quantised ahead of time")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: rows written into the owners' IPC-mapped buffers by this library's copy kernel, or "
+                         "NCCL all-to-alls plus a permutation pass")
+    ap.add_argument("--placement", choices=["balanced", "contiguous"], default="balanced",
+                    help="N > 1: experts assigned to ranks by greedy balancing of the expected load, or expert e on "
+                         "rank e // (E/N)")
+    ap.add_argument("--copy-ctas", type=int, default=0, help="CTAs of the peer copy kernel (0: one per SM)")
     ap.add_argument("--bind-cpus", type=int, default=0,
                     help="N > 1: 1 = pin each rank to the CPU cores NVML reports as local to its GPU")
-    ap.add_argument("--ep-reserve-sms", type=int, default=16, help="SMs wgrad leaves to the overlapped collective")
-    ap.add_argument("--experts", type=int, default=E_TOTAL, help="smaller case of the same workload (profiling)")
-    ap.add_argument("--rows", type=int, default=ROWS, help="smaller case of the same workload (profiling)")
+    ap.add_argument("--experts", type=int, default=0, help="smaller case of the same workload (profiling)")
+    ap.add_argument("--rows", type=int, default=0, help="smaller case of the same workload (profiling)")
     args = ap.parse_args()
-    E_TOTAL, ROWS = args.experts, args.rows
     if args.impl == "reference":
         run_reference(args)
+    elif not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in the product")
+    elif args.config in GROUPED:
+        run_grouped(args)
     else:
-        run_ours(args)
+        run_dense(args)
 
 
 if __name__ == "__main__":

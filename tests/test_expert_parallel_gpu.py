@@ -2,8 +2,9 @@
 same routed rows.  Forward output and activation gradient must be bit-identical (1x128 row scales
 and each output row do not depend on which other rows share a tile); weight gradients are compared
 within the GEMM gate because the 128-row column blocks are composed differently.
-Both forms are covered: the serial chain of autograd nodes and the single node that overlaps the
-weight quantisation and wgrad with the exchanges (same results bit for bit in out and grad_a).
+Three forms are covered: the serial chain of autograd nodes over NCCL all-to-alls, the single node that
+overlaps the weight quantisation and wgrad with the exchanges, and the peer-memory exchange that writes
+rows straight into the owners' buffers (same results bit for bit in out and grad_a).
 Cases that need more GPUs than are visible are skipped."""
 
 import os
@@ -42,11 +43,34 @@ def _worker(rank, store_path, q, overlap, WORLD):
         e_loc = E // WORLD
         x = xs[rank].cuda().requires_grad_(True)
         w_loc = w[rank * e_loc : (rank + 1) * e_loc].cuda().requires_grad_(True)
-        out = ep_grouped_gemm_fp8(x, w_loc, counts[rank].cuda(), config=cfg, overlap=overlap)
-        out.backward(gos[rank].cuda())
-        torch.cuda.synchronize()
+        if overlap == "peer":
+            # rows written straight into the owners' IPC-mapped buffers, two steps (regions are reused)
+            from primus_turbo_b200.pytorch.dist.expert_parallel import build_peer_plan, expert_parallel_apply_peer
+            from primus_turbo_b200.pytorch.dist.peer_exchange import PeerExchange
+            from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
+
+            host_group = dist.new_group(backend="gloo")
+            ex = PeerExchange(None, host_group, torch.device("cuda", rank), capacity_rows=int(counts.sum()),
+                              local_rows=int(counts.sum(1).max()))
+            for _ in range(2):
+                x.grad = w_loc.grad = None
+                plan = build_peer_plan(counts[rank], host_group, torch.device("cuda", rank))
+                out = expert_parallel_apply_peer(
+                    x, lambda rows, lens: grouped_gemm_fp8(rows, w_loc, lens, config=cfg), ex, plan)
+                out.backward(gos[rank].cuda())
+            torch.cuda.synchronize()
+            from primus_turbo_b200 import _lib
+
+            assert _lib.copy_segments_status() == 0
+        else:
+            out = ep_grouped_gemm_fp8(x, w_loc, counts[rank].cuda(), config=cfg, overlap=overlap)
+            out.backward(gos[rank].cuda())
+            torch.cuda.synchronize()
         q.put((rank, out.detach().float().cpu().tolist(), x.grad.float().cpu().tolist(), w_loc.grad.float().cpu().tolist()))
         dist.barrier()
+        if overlap == "peer":
+            ex.close()
+            dist.barrier()
     except Exception as exc:
         q.put((rank, repr(exc), None, None))
         raise
@@ -54,7 +78,7 @@ def _worker(rank, store_path, q, overlap, WORLD):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("overlap", [False, True])
+@pytest.mark.parametrize("overlap", [False, True, "peer"])
 @pytest.mark.parametrize("WORLD", [2, 4, 8])
 def test_expert_parallel_matches_single_gpu(overlap, WORLD):
     if torch.cuda.device_count() < WORLD:
