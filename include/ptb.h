@@ -123,13 +123,16 @@ int ptb_quant_fp8_block2d(const void *w, int w_dtype, int64_t B, int64_t M, int6
  *   rows up to a multiple of 128; s_col_padded [ceil((M+128*G)/128), N] on group-relative
  *   128-row blocks; var_k_lens[G] = ceil(len/128)*128 and its exclusive prefix var_k_offs[G+1].
  * Rows at or beyond group_offs[G] (row outputs) / var_k_offs[G] (padded outputs) are not written.
+ * block_table: optional workspace of ceil((M + 128*G) / 128) * 8 bytes (8-byte aligned), written by the
+ * call: with it every tile finds its source rows with one load; NULL makes every tile scan the G
+ * offsets instead (same results).
  * Replaces torch op quantize_fp8_blockwise_segment_m_row_col (bindings_pytorch.cpp:35,
  * quantization.cpp:1382-1439). */
 int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t N, int64_t G,
                                   const int64_t *group_lens, const int64_t *group_offs,
                                   void *q_row, void *q_col_padded, float *s_row,
                                   float *s_col_padded, int64_t *var_k_lens, int64_t *var_k_offs,
-                                  int q_dtype, ptb_stream_t stream);
+                                  void *block_table, int q_dtype, ptb_stream_t stream);
 
 /* ------------------------------------------------------------------ dequantize --------------- */
 /* out = cast(float(q) * scale_inv).  Replace dequantize_fp8_tensorwise / dequantize_fp8_rowwise

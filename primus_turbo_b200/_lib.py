@@ -41,7 +41,7 @@ _PROTOS = {
     "ptb_quant_fp8_block1d": [_P, _I, _L, _L, _I, _P, _I, _P, _P],
     "ptb_quant_fp8_block1d_dual": [_P, _I, _L, _L, _P, _P, _P, _P, _I, _P],
     "ptb_quant_fp8_block2d": [_P, _I, _L, _L, _L, _P, _I, _P, _P],
-    "ptb_quant_fp8_segment_row_col": [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P],
+    "ptb_quant_fp8_segment_row_col": [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "ptb_dequant_fp8_tensorwise": [_P, _I, _L, _P, _P, _I, _P],
     "ptb_dequant_fp8_rowwise": [_P, _I, _L, _L, _L, _P, _P, _I, _P],
     "ptb_dequant_fp8_block1d": [_P, _I, _L, _L, _I, _P, _P, _I, _P],

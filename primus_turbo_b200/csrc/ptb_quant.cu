@@ -79,6 +79,7 @@ struct BlockQuantArgs {
     int64_t G;
     const int64_t *group_offs;
     const int64_t *var_k_offs; // padded offsets, written by segment_offsets_kernel before the tile kernel runs
+    const int2 *block_table;   // optional: per padded 128-row block {first source row, end of its group's rows}
 };
 
 template <typename T> struct Packed2;
@@ -146,10 +147,14 @@ template <> struct RowFrag<float> {
     }
 };
 
-// var_k_lens[g] = ceil(len_g / 128) * 128 and its exclusive prefix var_k_offs[G+1] (one CTA).
+// var_k_lens[g] = ceil(len_g / 128) * 128 and its exclusive prefix var_k_offs[G+1] (one CTA).  With a
+// block table, also: for every 128-row block of the padded layout, the first source row it holds and
+// the end of its group's source rows -- so the tile kernel finds its rows with one load instead of
+// scanning the offsets of all groups.
 __global__ void __launch_bounds__(256) segment_offsets_kernel(const int64_t *__restrict__ group_offs, int64_t G,
                                                                int64_t *__restrict__ var_k_lens,
-                                                               int64_t *__restrict__ var_k_offs) {
+                                                               int64_t *__restrict__ var_k_offs,
+                                                               int2 *__restrict__ block_table) {
     __shared__ int64_t s_scan[256];
     const int tid     = threadIdx.x;
     const int64_t per = cdiv<int64_t>(G, 256);
@@ -166,9 +171,14 @@ __global__ void __launch_bounds__(256) segment_offsets_kernel(const int64_t *__r
     }
     int64_t run = s_scan[tid] - local;
     for (int64_t g = g0; g < g1; ++g) {
-        const int64_t pl = cdiv<int64_t>(group_offs[g + 1] - group_offs[g], kBlk) * kBlk;
+        const int64_t gs = group_offs[g], ge = group_offs[g + 1];
+        const int64_t pl = cdiv<int64_t>(ge - gs, kBlk) * kBlk;
         var_k_lens[g]    = pl;
         var_k_offs[g]    = run;
+        if (block_table != nullptr) {
+            for (int64_t t = 0; t < pl / kBlk; ++t)
+                block_table[run / kBlk + t] = make_int2((int) (gs + t * kBlk), (int) ge);
+        }
         run += pl;
     }
     if (tid == 255) var_k_offs[G] = s_scan[255];
@@ -201,23 +211,33 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
     const int64_t out_row0 = tm * kBlk;
 
     if constexpr (SEGMENT) {
-        // find the group whose padded segment [var_k_offs[g], var_k_offs[g+1]) holds this tile
-        // (all four offsets of a candidate group are fetched in one round of independent loads, and a
-        // single barrier both publishes the hit and tells every thread whether there was one)
+        // find the source rows of this padded tile
         const int64_t block_start = tm * kBlk;
-        int found                 = 0;
-        for (int64_t g = tid; g < p.G; g += 256) {
-            const int64_t ps = p.var_k_offs[g], pe = p.var_k_offs[g + 1];
-            const int64_t gs = p.group_offs[g], ge = p.group_offs[g + 1];
-            if (block_start >= ps && block_start < pe) {
-                found    = 1;
-                s_seg[1] = gs + (block_start - ps);
-                s_seg[2] = ge;
+        if (p.block_table != nullptr) {
+            // one load from the table written by the offsets kernel; tiles beyond the last padded
+            // segment have nothing to do
+            if (block_start >= p.var_k_offs[p.G]) return;
+            const int2 e = p.block_table[tm];
+            in_row0 = e.x;
+            in_end  = e.y;
+        } else {
+            // no table: scan the groups (all four offsets of a candidate group are fetched in one round of
+            // independent loads, and a single barrier both publishes the hit and tells every thread
+            // whether there was one)
+            int found = 0;
+            for (int64_t g = tid; g < p.G; g += 256) {
+                const int64_t ps = p.var_k_offs[g], pe = p.var_k_offs[g + 1];
+                const int64_t gs = p.group_offs[g], ge = p.group_offs[g + 1];
+                if (block_start >= ps && block_start < pe) {
+                    found    = 1;
+                    s_seg[1] = gs + (block_start - ps);
+                    s_seg[2] = ge;
+                }
             }
+            if (!__syncthreads_or(found)) return; // tile lies beyond the last padded segment
+            in_row0 = s_seg[1];
+            in_end  = s_seg[2];
         }
-        if (!__syncthreads_or(found)) return; // tile lies beyond the last padded segment
-        in_row0 = s_seg[1];
-        in_end  = s_seg[2];
     }
 
     const T *xb        = reinterpret_cast<const T *>(p.x) + b * p.M * p.N;
@@ -915,7 +935,7 @@ int ptb_quant_fp8_block2d(const void *w, int w_dtype, int64_t B, int64_t M, int6
 int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t N, int64_t G,
                                   const int64_t *group_lens, const int64_t *group_offs, void *q_row,
                                   void *q_col_padded, float *s_row, float *s_col_padded, int64_t *var_k_lens,
-                                  int64_t *var_k_offs, int q_dtype, ptb_stream_t stream) {
+                                  int64_t *var_k_offs, void *block_table, int q_dtype, ptb_stream_t stream) {
     (void) group_lens; // lengths are implied by the offsets
     PTB_REQUIRE(M >= 0 && N >= 0 && G >= 0, PTB_ERR_ARG, "quant_segment_row_col: negative size");
     PTB_REQUIRE(group_offs && var_k_lens && var_k_offs, PTB_ERR_ARG, "quant_segment_row_col: null group arrays");
@@ -928,7 +948,11 @@ int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t
     a.s_row_stride_m = 1; a.s_row_stride_nb = M; // row scales stored [ceil(N/128), M]
     a.q_col = (uint8_t *) q_col_padded; a.s_col = s_col_padded;
     a.group_offs = group_offs; a.var_k_offs = var_k_offs;
-    segment_offsets_kernel<<<1, 256, 0, (cudaStream_t) stream>>>(group_offs, G, var_k_lens, var_k_offs);
+    PTB_REQUIRE(block_table == nullptr || M < 2147483647LL, PTB_ERR_TOO_LARGE,
+                "quant_segment_row_col: the block table holds 32-bit row numbers");
+    a.block_table = (const int2 *) block_table;
+    segment_offsets_kernel<<<1, 256, 0, (cudaStream_t) stream>>>(group_offs, G, var_k_lens, var_k_offs,
+                                                                  (int2 *) block_table);
     PTB_LAUNCH_CHECK("segment_offsets_kernel");
     if (M == 0) return 0;
     return launch_block_quant<kModeRow | kModeCol, true>(a, x_dtype, q_dtype, (cudaStream_t) stream);

@@ -169,11 +169,13 @@ def quant_fp8_blockwise_segment_m_row_col_impl(
     s_col = torch.empty((ceil_div(m_pad, block_size), N), dtype=torch.float32, device=dev)
     vk_lens = torch.empty(G, dtype=torch.int64, device=dev)
     vk_offs = torch.empty(G + 1, dtype=torch.int64, device=dev)
+    # workspace: per padded 128-row block, where its source rows start and end (written by the call)
+    table = torch.empty((ceil_div(m_pad, block_size), 2), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         _lib.call(
             "ptb_quant_fp8_segment_row_col", ptr(x), dtype_code(x.dtype), M, N, G,
             ptr(group_lens.contiguous()), ptr(group_offs.contiguous()), ptr(q_row), ptr(q_col), ptr(s_row),
-            ptr(s_col), ptr(vk_lens), ptr(vk_offs), dtype_code(dtype), stream_of(x),
+            ptr(s_col), ptr(vk_lens), ptr(vk_offs), ptr(table), dtype_code(dtype), stream_of(x),
         )
     return q_row, q_col, s_row, s_col, vk_lens, vk_offs
 

@@ -223,3 +223,32 @@ def test_blockwise_kernels_match_reference_triton_fixture():
     GU.assert_scales_equal(s_col[: pu // 128], GU.f32(z["seg_s_col"])[: pu // 128].contiguous(), "segment column scales")
     GU.assert_payload_matches(q_col[:pu], GU.u8(z["seg_q_col"])[:pu], xp, GU.forward_scale(xp, "col"),
                               "segment column copy")
+
+
+def test_segment_row_col_without_block_table_gives_the_same_bytes():
+    """The per-block source-row table is an optional workspace: with NULL every tile scans the group
+    offsets instead, and all six outputs must be identical."""
+    from primus_turbo_b200 import _lib
+
+    gl = torch.tensor([100, 0, 256, 1, 300, 129], dtype=torch.int64)
+    m, n = int(gl.sum()) + 5, 384
+    x = randn(gen(9), m, n).to(DEV)
+    gld = gl.to(DEV)
+    offs = group_offs_from_lens(gld)
+    with_table = quant_fp8_blockwise_segment_m_row_col_impl(x, E4, 128, gld, offs)
+    G_, m_pad = gl.numel(), m + 128 * gl.numel()
+    q_row = torch.zeros((m, n), dtype=E4, device=DEV)
+    q_col = torch.zeros((m_pad, n), dtype=E4, device=DEV)
+    s_row = torch.zeros((3, m), dtype=torch.float32, device=DEV)
+    s_col = torch.zeros(((m_pad + 127) // 128, n), dtype=torch.float32, device=DEV)
+    vk_lens = torch.zeros(G_, dtype=torch.int64, device=DEV)
+    vk_offs = torch.zeros(G_ + 1, dtype=torch.int64, device=DEV)
+    _lib.call("ptb_quant_fp8_segment_row_col", x.data_ptr(), _lib.PTB_BF16, m, n, G_, gld.data_ptr(), offs.data_ptr(),
+              q_row.data_ptr(), q_col.data_ptr(), s_row.data_ptr(), s_col.data_ptr(), vk_lens.data_ptr(),
+              vk_offs.data_ptr(), None, _lib.PTB_E4M3, torch.cuda.current_stream().cuda_stream)
+    mu, pu = int(gl.sum()), int(vk_offs[-1])
+    assert torch.equal(vk_offs, with_table[5]) and torch.equal(vk_lens, with_table[4])
+    assert torch.equal(q_row[:mu].view(torch.uint8), with_table[0][:mu].view(torch.uint8))
+    assert torch.equal(q_col[:pu].view(torch.uint8), with_table[1][:pu].view(torch.uint8))
+    assert torch.equal(s_row[:, :mu], with_table[2][:, :mu])
+    assert torch.equal(s_col[: pu // 128], with_table[3][: pu // 128])
