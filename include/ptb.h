@@ -186,6 +186,38 @@ int ptb_copy_segments_status(int *status, int reset);
 int ptb_gather_rows(const void *in, const int64_t *index, int64_t n_out, int64_t n_in,
                     int64_t row_bytes, void *out, ptb_stream_t stream);
 
+/* MoE token permutation, index part.  routing_map [T, E], one byte per entry (non-zero: token t is routed
+ * to expert e).  Writes row_id_map [T, E] int32 -- the row of (t, e) in the expert-major permuted order
+ * (experts in increasing id, tokens in increasing id inside an expert), or -1 where the token is not
+ * routed or the row falls at or beyond `capacity` -- tokens_per_expert [E] int64 and, if non-NULL,
+ * sorted_indices [capacity] int64 (the token id of every permuted row; rows past the routed total are
+ * left untouched).  workspace: ceil(T/256) * E * 4 bytes rounded up to 16, plus (E + 1) * 8 bytes.
+ * E <= 1024.  Replaces permutation.make_row_id_map and the mask-to-index part of token_permute
+ * (primus_turbo/pytorch/ops/moe/permutation.py:18-112,281-369; csrc/kernels/moe_permute/moe_permute.cu). */
+int ptb_moe_row_id_map(const void *routing_map, int64_t T, int64_t E, int64_t capacity,
+                       int32_t *row_id_map, int64_t *tokens_per_expert, int64_t *sorted_indices,
+                       void *workspace, ptb_stream_t stream);
+
+/* out[i, :] = cast(float(in[index[i], :]) * weights[i]) over rows of H elements of type dtype (PTB_F32 /
+ * PTB_F16 / PTB_BF16); an index outside [0, n_in) writes a zero row.  The backward pass of the weighted
+ * un-permute (permutation.py:151-279 in the reference). */
+int ptb_gather_rows_scaled(const void *in, int dtype, const int64_t *index, const float *weights,
+                           int64_t n_out, int64_t n_in, int64_t H, void *out, ptb_stream_t stream);
+
+/* Un-permute: out[t, :] = sum over the experts e with row_id_map[t, e] >= 0, in increasing e, of
+ * in[row_id_map[t, e], :] * (probs ? probs[t, e] : 1), accumulated in fp32 with separate multiply and
+ * add (the value a sequential fp32 scatter-add gives), cast to dtype.  probs: fp32 [T, E] or NULL.
+ * Replaces token_unpermute's scatter_add (permutation.py:371-436). */
+int ptb_unpermute_rows(const void *in, int dtype, const int32_t *row_id_map, const float *probs,
+                       int64_t T, int64_t E, int64_t H, void *out, ptb_stream_t stream);
+
+/* Backward of ptb_unpermute_rows: grad_in[row_id_map[t, e], :] = grad_out[t, :] * p(t, e) and, if
+ * grad_probs is non-NULL, grad_probs[t, e] = dot(grad_out[t, :], fwd_in[row_id_map[t, e], :]) (0 where
+ * the token is not routed).  Rows of grad_in no token maps to are left untouched. */
+int ptb_unpermute_rows_bwd(const void *grad_out, int dtype, const void *fwd_in,
+                           const int32_t *row_id_map, const float *probs, int64_t T, int64_t E,
+                           int64_t H, void *grad_in, float *grad_probs, ptb_stream_t stream);
+
 /* ------------------------------------------------------------------ GEMM --------------------- */
 /* C[M,N] = op(A)[M,K] . op(B)[K,N], FP8 operands, fp32 accumulation, c_dtype output.
  *   a: [M,K] (trans_a = 0, lda = row pitch in elements) or [K,M] (trans_a = 1)

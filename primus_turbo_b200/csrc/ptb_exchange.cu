@@ -115,6 +115,148 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t *__restr
     }
 }
 
+// ---- MoE token permutation: routing map -> expert-major positions --------------------------------------
+// routing_map [T, E] (one byte per entry, non-zero = token t goes to expert e).  Position of (t, e) in
+// the permuted order = rows of experts below e + tokens below t routed to e: a stable counting sort in
+// three passes over blocks of kTokBlock tokens (count per block and expert, scan, assign).
+constexpr int kTokBlock = 256;
+
+__global__ void __launch_bounds__(256) moe_count_kernel(const uint8_t *__restrict__ map, int64_t T, int64_t E,
+                                                         int *__restrict__ block_counts) {
+    const int64_t t0 = (int64_t) blockIdx.x * kTokBlock, t1 = imin(t0 + kTokBlock, T);
+    for (int64_t e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int64_t t = t0; t < t1; ++t) c += map[t * E + e] != 0;
+        block_counts[(int64_t) blockIdx.x * E + e] = c;
+    }
+}
+
+// one CTA: per expert, exclusive scan of the block counts over the token blocks; then the experts' first
+// positions (exclusive scan over experts, done by thread 0: E is at most a few thousand)
+__global__ void __launch_bounds__(256) moe_scan_kernel(int *__restrict__ block_counts, int64_t B, int64_t E,
+                                                        int64_t *__restrict__ tokens_per_expert,
+                                                        int64_t *__restrict__ expert_start) {
+    for (int64_t e = threadIdx.x; e < E; e += blockDim.x) {
+        int run = 0;
+        for (int64_t b = 0; b < B; ++b) {
+            const int c              = block_counts[b * E + e];
+            block_counts[b * E + e] = run;
+            run += c;
+        }
+        tokens_per_expert[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int64_t run = 0;
+        for (int64_t e = 0; e < E; ++e) {
+            expert_start[e] = run;
+            run += tokens_per_expert[e];
+        }
+        expert_start[E] = run;
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_assign_kernel(const uint8_t *__restrict__ map, int64_t T, int64_t E,
+                                                          const int *__restrict__ block_counts,
+                                                          const int64_t *__restrict__ expert_start, int64_t capacity,
+                                                          int *__restrict__ row_id_map,
+                                                          int64_t *__restrict__ sorted_indices) {
+    const int64_t t0 = (int64_t) blockIdx.x * kTokBlock, t1 = imin(t0 + kTokBlock, T);
+    for (int64_t e = threadIdx.x; e < E; e += blockDim.x) {
+        int64_t pos = expert_start[e] + block_counts[(int64_t) blockIdx.x * E + e];
+        for (int64_t t = t0; t < t1; ++t) {
+            int id = -1;
+            if (map[t * E + e] != 0) {
+                if (pos < capacity) {
+                    id = (int) pos;
+                    if (sorted_indices != nullptr) sorted_indices[pos] = t;
+                }
+                ++pos;
+            }
+            row_id_map[t * E + e] = id;
+        }
+    }
+}
+
+// ---- weighted row gather: out[i] = cast(float(in[index[i]]) * w[i]) ---------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gather_rows_scaled_kernel(const T *__restrict__ in, const int64_t *__restrict__ index,
+                                                                  const float *__restrict__ weights, int64_t n_out,
+                                                                  int64_t n_in, int64_t H, T *__restrict__ out) {
+    const int lane   = threadIdx.x & 31;
+    const int64_t w  = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nw = ((int64_t) gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = w; r < n_out; r += nw) {
+        const int64_t s = index[r];
+        const float wt  = weights[r];
+        const bool ok   = s >= 0 && s < n_in;
+        for (int64_t j = lane; j < H; j += 32)
+            out[r * H + j] = from_f32<T>(ok ? __fmul_rn(to_f32(in[s * H + j]), wt) : 0.0f);
+    }
+}
+
+// ---- un-permute: out[t] = sum over the experts e of token t, in increasing e, of in[pos(t,e)] * p(t,e) ------
+// One warp per token.  The (at most E) positions of the token are compacted into shared memory first,
+// then every lane walks its columns once per position.  Products and sums are separate fp32 operations
+// (no contraction), accumulated in expert order: the result equals a sequential fp32 scatter-add.
+constexpr int kUnpermWarps = 4;
+constexpr int kMaxExperts  = 1024;
+
+template <typename T, bool WITH_GRAD>
+__global__ void __launch_bounds__(kUnpermWarps * 32) unpermute_kernel(
+    const T *__restrict__ in, const int *__restrict__ row_id_map, const float *__restrict__ probs, int64_t T_, int64_t E,
+    int64_t H, T *__restrict__ out,
+    // WITH_GRAD: `in` is the gradient of the un-permuted rows [T, H], `fwd_in` the permuted rows of the
+    // forward pass; writes grad_in[pos] = g[t] * p and grad_probs[t, e] = dot(g[t], fwd_in[pos])
+    const T *__restrict__ fwd_in, float *__restrict__ grad_probs) {
+    __shared__ int s_pos[kUnpermWarps][kMaxExperts];
+    __shared__ int s_exp[kUnpermWarps][kMaxExperts];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t t = (int64_t) blockIdx.x * kUnpermWarps + warp;
+    if (t >= T_) return;
+    int n = 0;
+    for (int64_t base = 0; base < E; base += 32) {
+        const int64_t e = base + lane;
+        const int id    = e < E ? row_id_map[t * E + e] : -1;
+        const unsigned m = __ballot_sync(0xffffffffu, id >= 0);
+        if (id >= 0) {
+            const int k  = n + __popc(m & ((1u << lane) - 1));
+            s_pos[warp][k] = id;
+            s_exp[warp][k] = (int) e;
+        }
+        if (WITH_GRAD && grad_probs != nullptr && e < E && id < 0) grad_probs[t * E + e] = 0.0f;
+        n += __popc(m);
+    }
+    __syncwarp();
+    if constexpr (!WITH_GRAD) {
+        for (int64_t j = lane; j < H; j += 32) {
+            float acc = 0.0f;
+            for (int k = 0; k < n; ++k) {
+                float v = to_f32(in[(int64_t) s_pos[warp][k] * H + j]);
+                if (probs != nullptr) v = __fmul_rn(v, probs[t * E + s_exp[warp][k]]);
+                acc = __fadd_rn(acc, v);
+            }
+            out[t * H + j] = from_f32<T>(acc);
+        }
+    } else {
+        for (int k = 0; k < n; ++k) {
+            const int64_t pos = s_pos[warp][k];
+            const float p     = probs != nullptr ? probs[t * E + s_exp[warp][k]] : 1.0f;
+            float dot         = 0.0f;
+            for (int64_t j = lane; j < H; j += 32) {
+                const float g = to_f32(in[t * H + j]);
+                out[pos * H + j] = from_f32<T>(__fmul_rn(g, p));
+                if (grad_probs != nullptr) dot += g * to_f32(fwd_in[pos * H + j]);
+            }
+            if (grad_probs != nullptr) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (lane == 0) grad_probs[t * E + s_exp[warp][k]] = dot;
+            }
+        }
+    }
+}
+
 } // namespace
 } // namespace ptb
 
@@ -173,6 +315,73 @@ int ptb_gather_rows(const void *in, const int64_t *index, int64_t n_out, int64_t
     gather_rows_kernel<<<blocks, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) in, index, n_out, n_in, row_bytes,
                                                                    (uint8_t *) out);
     PTB_LAUNCH_CHECK("gather_rows_kernel");
+    return 0;
+}
+
+int ptb_moe_row_id_map(const void *routing_map, int64_t T, int64_t E, int64_t capacity, int32_t *row_id_map,
+                       int64_t *tokens_per_expert, int64_t *sorted_indices, void *workspace, ptb_stream_t stream) {
+    PTB_REQUIRE(T >= 0 && E >= 0 && capacity >= 0, PTB_ERR_ARG, "moe_row_id_map: negative size");
+    PTB_REQUIRE(E <= kMaxExperts, PTB_ERR_TOO_LARGE, "moe_row_id_map: at most %d experts", kMaxExperts);
+    PTB_REQUIRE(T * E < 2147483647LL && capacity < 2147483647LL, PTB_ERR_TOO_LARGE, "moe_row_id_map: problem too large");
+    if (E == 0) return 0;
+    PTB_REQUIRE(tokens_per_expert && workspace, PTB_ERR_ARG, "moe_row_id_map: null pointer");
+    const int64_t B = cdiv<int64_t>(T, kTokBlock);
+    int *block_counts     = (int *) workspace;                               // [B, E] int32
+    int64_t *expert_start = (int64_t *) ((uint8_t *) workspace + ((B * E * 4 + 15) / 16) * 16); // [E + 1] int64
+    cudaStream_t st = (cudaStream_t) stream;
+    if (T > 0) {
+        PTB_REQUIRE(routing_map && row_id_map, PTB_ERR_ARG, "moe_row_id_map: null pointer");
+        moe_count_kernel<<<(unsigned) B, 256, 0, st>>>((const uint8_t *) routing_map, T, E, block_counts);
+        PTB_LAUNCH_CHECK("moe_count_kernel");
+    }
+    moe_scan_kernel<<<1, 256, 0, st>>>(block_counts, B, E, tokens_per_expert, expert_start);
+    PTB_LAUNCH_CHECK("moe_scan_kernel");
+    if (T > 0) {
+        moe_assign_kernel<<<(unsigned) B, 256, 0, st>>>((const uint8_t *) routing_map, T, E, block_counts, expert_start,
+                                                         capacity, row_id_map, sorted_indices);
+        PTB_LAUNCH_CHECK("moe_assign_kernel");
+    }
+    return 0;
+}
+
+int ptb_gather_rows_scaled(const void *in, int dtype, const int64_t *index, const float *weights, int64_t n_out,
+                           int64_t n_in, int64_t H, void *out, ptb_stream_t stream) {
+    PTB_REQUIRE(n_out >= 0 && n_in >= 0 && H >= 0, PTB_ERR_ARG, "gather_rows_scaled: negative size");
+    if (n_out == 0 || H == 0) return 0;
+    PTB_REQUIRE(index && weights && out && (n_in == 0 || in), PTB_ERR_ARG, "gather_rows_scaled: null pointer");
+    const int blocks = (int) imin(cdiv<int64_t>(n_out, 8), 148 * 16);
+    PTB_SWITCH_HP(dtype, T, (gather_rows_scaled_kernel<T><<<blocks, 256, 0, (cudaStream_t) stream>>>(
+                                (const T *) in, index, weights, n_out, n_in, H, (T *) out)));
+    PTB_LAUNCH_CHECK("gather_rows_scaled_kernel");
+    return 0;
+}
+
+int ptb_unpermute_rows(const void *in, int dtype, const int32_t *row_id_map, const float *probs, int64_t T, int64_t E,
+                       int64_t H, void *out, ptb_stream_t stream) {
+    PTB_REQUIRE(T >= 0 && E >= 0 && H >= 0, PTB_ERR_ARG, "unpermute_rows: negative size");
+    PTB_REQUIRE(E <= kMaxExperts, PTB_ERR_TOO_LARGE, "unpermute_rows: at most %d experts", kMaxExperts);
+    if (T == 0 || H == 0) return 0;
+    PTB_REQUIRE(out && row_id_map, PTB_ERR_ARG, "unpermute_rows: null pointer");
+    const unsigned grid = (unsigned) cdiv<int64_t>(T, kUnpermWarps);
+    PTB_SWITCH_HP(dtype, TT, (unpermute_kernel<TT, false><<<grid, kUnpermWarps * 32, 0, (cudaStream_t) stream>>>(
+                                 (const TT *) in, row_id_map, probs, T, E, H, (TT *) out, nullptr, nullptr)));
+    PTB_LAUNCH_CHECK("unpermute_kernel");
+    return 0;
+}
+
+int ptb_unpermute_rows_bwd(const void *grad_out, int dtype, const void *fwd_in, const int32_t *row_id_map,
+                           const float *probs, int64_t T, int64_t E, int64_t H, void *grad_in, float *grad_probs,
+                           ptb_stream_t stream) {
+    PTB_REQUIRE(T >= 0 && E >= 0 && H >= 0, PTB_ERR_ARG, "unpermute_rows_bwd: negative size");
+    PTB_REQUIRE(E <= kMaxExperts, PTB_ERR_TOO_LARGE, "unpermute_rows_bwd: at most %d experts", kMaxExperts);
+    if (T == 0 || H == 0) return 0;
+    PTB_REQUIRE(grad_out && grad_in && row_id_map, PTB_ERR_ARG, "unpermute_rows_bwd: null pointer");
+    PTB_REQUIRE(grad_probs == nullptr || fwd_in != nullptr, PTB_ERR_ARG, "unpermute_rows_bwd: grad_probs needs the forward rows");
+    const unsigned grid = (unsigned) cdiv<int64_t>(T, kUnpermWarps);
+    PTB_SWITCH_HP(dtype, TT, (unpermute_kernel<TT, true><<<grid, kUnpermWarps * 32, 0, (cudaStream_t) stream>>>(
+                                 (const TT *) grad_out, row_id_map, probs, T, E, H, (TT *) grad_in, (const TT *) fwd_in,
+                                 grad_probs)));
+    PTB_LAUNCH_CHECK("unpermute_kernel");
     return 0;
 }
 
