@@ -134,6 +134,33 @@ int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t
                                   float *s_col_padded, int64_t *var_k_lens, int64_t *var_k_offs,
                                   void *block_table, int q_dtype, ptb_stream_t stream);
 
+/* SwiGLU with routing probabilities: out[t, j] = (u / (1 + exp(-u))) * x[t, H + j] * probs[t], u = x[t, j],
+ * x [rows, 2H] bf16 / fp16, probs fp32 [rows], row_mask int64 [rows] or NULL (0: the row is written as zeros);
+ * fp32 arithmetic, one rounding to dtype.  H % 8 == 0.
+ * Replaces swiglu_fwd_with_probs (primus_turbo/pytorch/kernels/activation/swiglu_impl.py:20-57,
+ * primus_turbo/triton/activation/swiglu_kernel.py:11-57,145-184). */
+int ptb_swiglu_probs_fwd(const void *x, int dtype, const float *probs, const int64_t *row_mask,
+                         int64_t rows, int64_t H, void *out, ptb_stream_t stream);
+
+/* Backward of the above: grad_x [rows, 2H] and grad_probs [rows] = sum_j grad_out * silu(u) * x[t, H + j].
+ * Replaces swiglu_bwd_with_probs (swiglu_impl.py:60-111, swiglu_kernel.py:60-142,187-248). */
+int ptb_swiglu_probs_bwd(const void *grad_out, const void *x, int dtype, const float *probs,
+                         const int64_t *row_mask, int64_t rows, int64_t H, void *grad_x,
+                         float *grad_probs, ptb_stream_t stream);
+
+/* ptb_quant_fp8_segment_row_col applied to SwiGLU-with-probabilities of x [M, 2N] without writing the
+ * activation: every tile computes act = round_to_dtype(swiglu(x)) in registers and quantises it, so the
+ * six outputs equal ptb_swiglu_probs_fwd followed by ptb_quant_fp8_segment_row_col byte for byte while
+ * moving 6 instead of 10 bytes per activation element.  N % 8 == 0; x bf16 / fp16, 16-byte aligned.
+ * Fuses the reference's swiglu_with_probs (primus_turbo/pytorch/ops/activation.py:23-83) with its
+ * grouped activation quantise (quantization_impl.py:379-464); the reference runs them as two kernels. */
+int ptb_swiglu_quant_fp8_segment_row_col(const void *x, int x_dtype, const float *probs, int64_t M,
+                                         int64_t N, int64_t G, const int64_t *group_offs,
+                                         void *q_row, void *q_col_padded, float *s_row,
+                                         float *s_col_padded, int64_t *var_k_lens,
+                                         int64_t *var_k_offs, void *block_table, int q_dtype,
+                                         ptb_stream_t stream);
+
 /* ------------------------------------------------------------------ dequantize --------------- */
 /* out = cast(float(q) * scale_inv).  Replace dequantize_fp8_tensorwise / dequantize_fp8_rowwise
  * (bindings_pytorch.cpp:43-46) and primus_turbo::dequant_fp8_blockwise_impl /

@@ -112,6 +112,14 @@ __device__ __forceinline__ void scale_from_amax(float amax, float eps, float &sc
     scale_inv = __fdiv_rn(1.0f, scale);
 }
 
+// SwiGLU with routing probability, one element: (up / (1 + exp(-up))) * down * prob in fp32
+// (primus_turbo/triton/activation/swiglu_kernel.py:49-55 in the reference).  Every kernel that needs
+// the activation calls this one function, so fused and unfused paths agree bit for bit.
+__device__ __forceinline__ float swiglu_prob(float up, float down, float prob) {
+    const float silu = __fdiv_rn(up, 1.0f + expf(-up));
+    return __fmul_rn(__fmul_rn(silu, down), prob);
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -80,7 +80,28 @@ struct BlockQuantArgs {
     const int64_t *group_offs;
     const int64_t *var_k_offs; // padded offsets, written by segment_offsets_kernel before the tile kernel runs
     const int2 *block_table;   // optional: per padded 128-row block {first source row, end of its group's rows}
+    // fused activation (ACT = 1): x is [M, 2N] (gate half, then linear half), the tile that is quantised is
+    // swiglu_prob(x[:, :N], x[:, N:], act_probs[row]) rounded to the input type first
+    const float *act_probs;
+    int64_t x_ld; // row pitch of x in elements (N, or 2N with the fused activation)
 };
+
+// 8 consecutive elements of the tile's source row `r`, columns col .. col+7 (all in range), as stored bits
+template <typename T, int ACT>
+__device__ __forceinline__ uint4 load_tile8(const T *__restrict__ xrow, int64_t col, int64_t N, float prob) {
+    if constexpr (ACT == 0) {
+        return *reinterpret_cast<const uint4 *>(xrow + col);
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4 *>(xrow + col);
+        const uint4 d = *reinterpret_cast<const uint4 *>(xrow + N + col);
+        const T *ue = reinterpret_cast<const T *>(&u), *de = reinterpret_cast<const T *>(&d);
+        uint4 o;
+        T *oe = reinterpret_cast<T *>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) oe[i] = from_f32<T>(swiglu_prob(to_f32(ue[i]), to_f32(de[i]), prob));
+        return o;
+    }
+}
 
 template <typename T> struct Packed2;
 template <> struct Packed2<__nv_bfloat16> {
@@ -186,7 +207,7 @@ __global__ void __launch_bounds__(256) segment_offsets_kernel(const int64_t *__r
 
 // Grid: one CTA per 128x128 tile, column tiles fastest, so that CTAs resident together stream whole
 // contiguous row bands (DRAM pages are used end to end instead of 256 bytes at a time).
-template <typename T, int FMT, int MODE, bool SEGMENT>
+template <typename T, int FMT, int MODE, bool SEGMENT, int ACT = 0>
 __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArgs p) {
     __shared__ float s_colmax[16][kBlk + 1];
     __shared__ float s_colscale[kBlk];
@@ -240,7 +261,7 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
         }
     }
 
-    const T *xb        = reinterpret_cast<const T *>(p.x) + b * p.M * p.N;
+    const T *xb        = reinterpret_cast<const T *>(p.x) + b * p.M * p.x_ld;
     const int64_t col  = tn * kBlk + tx * 8;
     const bool vec_in  = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15u) == 0);
     const bool vec_out = (p.N % 8 == 0);
@@ -294,11 +315,15 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
         // Same arithmetic, same results.
         if (vec_in && in_row0 + kBlk <= in_end && (tn + 1) * kBlk <= p.N) {
             using T2 = typename Packed2<T>::type;
-            const T *src       = xb + (in_row0 + ty) * p.N + col;
-            const int64_t step = 16 * p.N;
+            const T *src       = xb + (in_row0 + ty) * p.x_ld;
+            const int64_t step = 16 * p.N; // row step of the outputs (16 rows of N columns)
             uint4 raw[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4 *>(src + i * step);
+            for (int i = 0; i < 8; ++i) {
+                float prob = 1.0f;
+                if constexpr (ACT != 0) prob = p.act_probs[in_row0 + ty + 16 * i];
+                raw[i] = load_tile8<T, ACT>(src + (int64_t) (16 * i) * p.x_ld, col, p.N, prob);
+            }
             T2 cm2[4];
             float rm[8];
 #pragma unroll
@@ -372,8 +397,12 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int64_t r = in_row0 + ty + 16 * i;
-        if (r < in_end && col < p.N) frag[i].load(xb + r * p.N, col, p.N, vec_in);
-        else frag[i].zero();
+        if (r < in_end && col < p.N) {
+            if constexpr (ACT != 0) frag[i].raw = load_tile8<T, ACT>(xb + r * p.x_ld, col, p.N, p.act_probs[r]); // N % 8 == 0 here
+            else frag[i].load(xb + r * p.x_ld, col, p.N, vec_in);
+        } else {
+            frag[i].zero();
+        }
     }
     if constexpr (sizeof(T) == 2) {
         // |x| and max are exact in the storage format, so reduce two elements per instruction there
@@ -513,7 +542,8 @@ __global__ void __launch_bounds__(256, 3) quant_block_kernel(const BlockQuantArg
 }
 
 template <int MODE, bool SEGMENT>
-int launch_block_quant(const BlockQuantArgs &a, int x_dtype, int q_dtype, cudaStream_t st) {
+int launch_block_quant(BlockQuantArgs a, int x_dtype, int q_dtype, cudaStream_t st) {
+    if (a.x_ld == 0) a.x_ld = a.N;
     const int64_t rows = SEGMENT ? (a.M + a.G * kBlk) : a.M;
     const int64_t tiles_m = cdiv<int64_t>(rows, kBlk) * (SEGMENT ? 1 : a.B);
     const int64_t tiles_n = cdiv<int64_t>(a.N, kBlk);
@@ -956,6 +986,43 @@ int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t
     PTB_LAUNCH_CHECK("segment_offsets_kernel");
     if (M == 0) return 0;
     return launch_block_quant<kModeRow | kModeCol, true>(a, x_dtype, q_dtype, (cudaStream_t) stream);
+}
+
+int ptb_swiglu_quant_fp8_segment_row_col(const void *x, int x_dtype, const float *probs, int64_t M, int64_t N, int64_t G,
+                                         const int64_t *group_offs, void *q_row, void *q_col_padded, float *s_row,
+                                         float *s_col_padded, int64_t *var_k_lens, int64_t *var_k_offs,
+                                         void *block_table, int q_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(M >= 0 && N > 0 && G >= 0, PTB_ERR_ARG, "swiglu_quant_segment_row_col: bad size");
+    PTB_REQUIRE(N % 8 == 0, PTB_ERR_ALIGN, "swiglu_quant_segment_row_col: the hidden size must be a multiple of 8");
+    PTB_REQUIRE(x_dtype == PTB_BF16 || x_dtype == PTB_F16, PTB_ERR_ARG, "swiglu_quant_segment_row_col: x must be bf16 or fp16");
+    PTB_REQUIRE(group_offs && var_k_lens && var_k_offs, PTB_ERR_ARG, "swiglu_quant_segment_row_col: null group arrays");
+    PTB_REQUIRE(x && probs && q_row && q_col_padded && s_row && s_col_padded, PTB_ERR_ARG,
+                "swiglu_quant_segment_row_col: null pointer");
+    PTB_REQUIRE(aligned16(x), PTB_ERR_ALIGN, "swiglu_quant_segment_row_col: x must be 16-byte aligned");
+    PTB_REQUIRE(block_table == nullptr || M < 2147483647LL, PTB_ERR_TOO_LARGE,
+                "swiglu_quant_segment_row_col: the block table holds 32-bit row numbers");
+    BlockQuantArgs a{};
+    a.x = x; a.B = 1; a.M = M; a.N = N; a.G = G; a.x_ld = 2 * N; a.act_probs = probs;
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row;
+    a.s_row_stride_m = 1; a.s_row_stride_nb = M;
+    a.q_col = (uint8_t *) q_col_padded; a.s_col = s_col_padded;
+    a.group_offs = group_offs; a.var_k_offs = var_k_offs; a.block_table = (const int2 *) block_table;
+    cudaStream_t st = (cudaStream_t) stream;
+    segment_offsets_kernel<<<1, 256, 0, st>>>(group_offs, G, var_k_lens, var_k_offs, (int2 *) block_table);
+    PTB_LAUNCH_CHECK("segment_offsets_kernel");
+    if (M == 0) return 0;
+    const int64_t tiles_m = cdiv<int64_t>(M + G * kBlk, kBlk), tiles_n = cdiv<int64_t>(N, kBlk);
+    PTB_REQUIRE(tiles_n * tiles_m <= 2147483647LL, PTB_ERR_TOO_LARGE, "tile grid too large");
+    PTB_REQUIRE((reinterpret_cast<uintptr_t>(a.q_row) & 7u) == 0 && (reinterpret_cast<uintptr_t>(a.q_col) & 7u) == 0,
+                PTB_ERR_ALIGN, "blockwise quantise: FP8 output pointers must be 8-byte aligned");
+    const unsigned grid = (unsigned) (tiles_m * tiles_n);
+    if (x_dtype == PTB_BF16) {
+        PTB_SWITCH_FP8(q_dtype, FMT, (quant_block_kernel<__nv_bfloat16, FMT, kModeRow | kModeCol, true, 1><<<grid, 256, 0, st>>>(a)));
+    } else {
+        PTB_SWITCH_FP8(q_dtype, FMT, (quant_block_kernel<__half, FMT, kModeRow | kModeCol, true, 1><<<grid, 256, 0, st>>>(a)));
+    }
+    PTB_LAUNCH_CHECK("quant_block_kernel");
+    return 0;
 }
 
 int ptb_dequant_fp8_tensorwise(const void *q, int q_dtype, int64_t n, const float *scale_inv, void *out,
