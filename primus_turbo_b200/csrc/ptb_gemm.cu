@@ -910,6 +910,13 @@ int scale_mode_of(int granularity, int b_block_2d, int *mode) {
 } // namespace
 } // namespace ptb
 
+#include "ptb_gemm_wgrad.cuh"
+
+// Build-time switch for A/B measurements of the two wgrad kernels (1: paired-tile kernel where it applies).
+#ifndef PTB_WGRAD_PAIR
+#define PTB_WGRAD_PAIR 1
+#endif
+
 using namespace ptb;
 
 extern "C" {
@@ -1041,6 +1048,18 @@ int ptb_grouped_gemm_fp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_l
     if (rc) return rc;
     g.a_scale = lhs_scale; g.as_m = 1; g.as_k = OUT_M;
     g.b_scale = rhs_scale; g.bs_g = 0; g.bs_n = 1; g.bs_k = OUT_N;
+    if (PTB_WGRAD_PAIR && mode == kScaleBlock1D && OUT_M % 256 == 0 && OUT_N % 128 == 0 && g.use_tma_store &&
+        (out_dtype == PTB_BF16 || out_dtype == PTB_F16) && aligned16(lhs_scale) && aligned16(rhs_scale)) {
+        // blockwise wgrad on tile-aligned shapes: 256 x 128 paired tiles (see ptb_gemm_wgrad.cuh)
+        g.bn = 128;
+        g.idesc = make_idesc(lhs_dtype, rhs_dtype, 1, 1, 128);
+        int dev = 0, sms = 0;
+        PTB_CUDA(cudaGetDevice(&dev));
+        PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        const int grid = (num_sms > 0 && num_sms < sms) ? num_sms : sms;
+        return out_dtype == PTB_BF16 ? launch_wgrad_pair<__nv_bfloat16>(g, grid, (cudaStream_t) stream)
+                                     : launch_wgrad_pair<__half>(g, grid, (cudaStream_t) stream);
+    }
     return launch_gemm(g, mode, out_dtype, num_sms, (cudaStream_t) stream);
 }
 
