@@ -627,7 +627,12 @@ def run_grouped(args):
         from primus_turbo_b200.pytorch.dist.peer_exchange import PeerExchange
 
         cap = int(max(2 * ROWS // world, ROWS // world + 4096))
-        exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas)
+        try:
+            # checks, on the host and on every rank alike, that all GPUs of the job can address each other
+            exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas)
+        except RuntimeError as exc:
+            print(f"[bench] rank {rank}: {exc}; using NCCL all-to-alls", file=sys.stderr)
+            exchange, args.exchange = None, "nccl"
     state = {"exchange": exchange}
 
     def make_step(weight):
@@ -664,21 +669,6 @@ def run_grouped(args):
         torch.cuda.synchronize()
 
     ep_parity = None
-    if world > 1 and exchange is not None:
-        # one guarded step: if the peer mapping cannot be set up on this machine, every rank falls back to
-        # the all-to-all exchange (still this library's kernels on every GPU; nothing runs on the host)
-        try:
-            step(a, gy)
-            torch.cuda.synchronize()
-            ok = 1
-        except Exception as exc:  # noqa: BLE001
-            print(f"[bench] rank {rank}: peer exchange unavailable ({exc!r}); falling back to NCCL all-to-alls",
-                  file=sys.stderr)
-            ok = 0
-        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            state["exchange"], args.exchange = None, "nccl"
     if world > 1:
         nz = torch.nonzero(pos_counts > 0).flatten().tolist()
         sample = sorted({nz[0], nz[len(nz) // 3], nz[(2 * len(nz)) // 3], nz[-1]})

@@ -202,6 +202,13 @@ int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
                       const int64_t *segments, int64_t nseg, int64_t row_bytes, int num_ctas,
                       ptb_stream_t stream);
 
+/* Lets kernels launched on the current device address memory that lives on peer_device (a device index of
+ * this process): cudaDeviceEnablePeerAccess, treating "already enabled" as success.  Memory of another
+ * process opened through a CUDA IPC handle is mapped for the device that was current when it was
+ * opened; a kernel on a different device may only touch it after this call.  PTB_ERR_UNSUPPORTED when
+ * the two devices have no peer path.  No counterpart in the reference. */
+int ptb_enable_peer_access(int peer_device);
+
 /* Reads (and optionally clears) the flag a copy sets when its segment table named a bad
  * destination.  Synchronises with the device.  No counterpart in the reference. */
 int ptb_copy_segments_status(int *status, int reset);

@@ -54,6 +54,7 @@ _PROTOS = {
     "ptb_grouped_gemm_fp8_variable_k": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _I, _P],
     "ptb_copy_segments": [_P, _P, _I, _P, _L, _L, _I, _P],
     "ptb_copy_segments_status": [ctypes.POINTER(c_int), _I],
+    "ptb_enable_peer_access": [_I],
     "ptb_gather_rows": [_P, _P, _L, _L, _L, _P, _P],
     "ptb_swiglu_probs_fwd": [_P, _I, _P, _P, _L, _L, _P, _P],
     "ptb_swiglu_probs_bwd": [_P, _P, _I, _P, _P, _L, _L, _P, _P, _P],
@@ -103,7 +104,7 @@ def check(rc: int, what: str) -> None:
 # kernels enqueued by one successful call of each entry point (memset nodes not counted)
 KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_rowwise_noalloc": 2,
                     "ptb_quant_fp8_segment_row_col": 2, "ptb_moe_row_id_map": 3, "ptb_swiglu_quant_fp8_segment_row_col": 2,
-                    "ptb_gemm_status": 0, "ptb_copy_segments_status": 0}
+                    "ptb_gemm_status": 0, "ptb_copy_segments_status": 0, "ptb_enable_peer_access": 0}
 # PTB_DEBUG_STATUS=1: after every GEMM call, wait for the device and raise if a bounded wait inside the
 # kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
 _DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")

@@ -292,6 +292,22 @@ int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
     return 0;
 }
 
+int ptb_enable_peer_access(int peer_device) {
+    int dev = -1;
+    PTB_CUDA(cudaGetDevice(&dev));
+    if (peer_device == dev) return 0;
+    int can = 0;
+    PTB_CUDA(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+    PTB_REQUIRE(can, PTB_ERR_UNSUPPORTED, "device %d cannot address the memory of device %d", dev, peer_device);
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void) cudaGetLastError(); // not an error: clear it
+        return 0;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+    return 0;
+}
+
 int ptb_copy_segments_status(int *status, int reset) {
     PTB_REQUIRE(status, PTB_ERR_ARG, "copy_segments_status: null pointer");
     PTB_CUDA(cudaMemcpyFromSymbol(status, g_copy_error, sizeof(int)));

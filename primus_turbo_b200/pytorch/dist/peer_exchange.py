@@ -91,8 +91,20 @@ def _export_cuda_ipc(t: torch.Tensor):
 
 
 def _import_cuda_ipc(handle):
+    """Open another rank's region.  torch maps IPC memory with the OWNER's device index current, so the
+    mapping is addressable from that device of this process; kernels of this rank run on its own
+    device and need peer access to the owner's device enabled first -- without it the first store
+    through the pointer is an illegal address."""
+    from primus_turbo_b200 import _lib
+
     fn, args = handle
-    return fn(*args)
+    mine = torch.cuda.current_device()
+    t = fn(*args)
+    owner = t.device.index
+    if owner != mine:
+        with torch.cuda.device(mine):
+            _lib.call("ptb_enable_peer_access", owner)
+    return t
 
 
 class PeerExchange:
@@ -122,6 +134,30 @@ class PeerExchange:
         self._import = import_fn or _import_cuda_ipc
         self._regions: Dict[Tuple[str, int, str], Tuple[torch.Tensor, List, List[int]]] = {}
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.device.type == "cuda" and import_fn is None:
+            self._check_peer_paths()
+
+    def _check_peer_paths(self) -> None:
+        """Before any region exists: every rank tells the others which device it runs on and enables peer
+        access to each of them; a missing peer path raises here, on the host, on every rank."""
+        from primus_turbo_b200 import _lib
+
+        mine = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        devices: List = [None] * self.world
+        dist.all_gather_object(devices, int(mine), group=self.host_group)
+        problem = None
+        with torch.cuda.device(mine):
+            for d in sorted(set(devices)):
+                if d != mine:
+                    try:
+                        _lib.call("ptb_enable_peer_access", d)
+                    except _lib.PtbError as exc:
+                        problem = str(exc)
+        verdicts: List = [None] * self.world
+        dist.all_gather_object(verdicts, problem, group=self.host_group)
+        bad = [f"rank {r}: {v}" for r, v in enumerate(verdicts) if v]
+        if bad:
+            raise RuntimeError("peer-memory exchange unavailable: " + "; ".join(bad))
 
     # ---- regions ---------------------------------------------------------------------------------
     def _region(self, direction: str, row_bytes: int, phase: str = "fwd"):
