@@ -91,20 +91,21 @@ def _export_cuda_ipc(t: torch.Tensor):
 
 
 def _import_cuda_ipc(handle):
-    """Open another rank's region.  torch maps IPC memory with the OWNER's device index current, so the
-    mapping is addressable from that device of this process; kernels of this rank run on its own
-    device and need peer access to the owner's device enabled first -- without it the first store
-    through the pointer is an illegal address."""
-    from primus_turbo_b200 import _lib
+    """Open another rank's region for kernels of THIS rank's device.
 
+    ``cudaIpcOpenMemHandle`` maps the memory into the address space of the device that is current when
+    it is called.  torch's rebuild function makes the OWNER's device index current (its use case is a
+    consumer that keeps working on the producer's device); a mapping made that way is not addressable
+    from this rank's device -- the first store through it is an illegal address, peer access enabled or
+    not.  So the handle is opened with this rank's device in the owner's place: the driver then maps
+    the peer GPU's memory for this device and enables peer access as needed (the lazy-peer-access
+    flag torch passes), which is the pattern NCCL and every IPC-based collective use.  The returned
+    tensor claims this rank's device; it is only ever used as a raw destination pointer."""
     fn, args = handle
-    mine = torch.cuda.current_device()
-    t = fn(*args)
-    owner = t.device.index
-    if owner != mine:
-        with torch.cuda.device(mine):
-            _lib.call("ptb_enable_peer_access", owner)
-    return t
+    args = list(args)
+    assert fn.__name__ == "rebuild_cuda_tensor" and len(args) >= 8, "unexpected CUDA IPC handle format"
+    args[6] = torch.cuda.current_device()  # storage_device: the device that is current during the open
+    return fn(*args)
 
 
 class PeerExchange:
