@@ -786,12 +786,17 @@ def run_grouped(args):
         _finish_line(args, line, kernel_ms, roofs, clocks, launches, status)
     if world > 1:
         if exchange is not None:
-            dist.barrier()
-            exchange.close()
-            dist.barrier()
+            exchange.close()  # collective: peers' mappings first, own regions after everyone has let go
         if board is not None:
             board.close()
+        dist.barrier()
         dist.destroy_process_group()
+        # Everything is measured, printed and torn down.  Leave without running interpreter-exit destructors:
+        # with CUDA IPC mappings in play, torch's exit-time bookkeeping of shared CUDA storages was seen to
+        # crash a rank after its results were out (exit code -11), which a launcher reads as a failed run.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():

@@ -182,9 +182,23 @@ class PeerExchange:
         dist.all_reduce(self._flag, group=self.group)
 
     def close(self) -> None:
-        """Drop the mappings of the other ranks' regions (call before the process group is destroyed, so
-        that every rank releases its peers' memory while they still exist)."""
+        """Collective teardown (call before the process group is destroyed): every rank first drops its
+        mappings of the other ranks' regions, all ranks meet, and only then does a rank release its own
+        regions -- so no rank ever frees memory that a peer still has mapped, and no rank unmaps memory
+        whose owner has already gone."""
+        import gc
+
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        for key, (local, views, ptrs) in list(self._regions.items()):
+            self._regions[key] = (local, [], [])
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.ipc_collect()
+        dist.barrier(group=self.host_group)
         self._regions.clear()
+        gc.collect()
+        dist.barrier(group=self.host_group)
 
     def push(self, src: torch.Tensor, segs: torch.Tensor, direction: str, rows_received: int,
              phase: str = "fwd") -> torch.Tensor:

@@ -70,7 +70,6 @@ def _worker(rank, store_path, q, overlap, WORLD):
         dist.barrier()
         if overlap == "peer":
             ex.close()
-            dist.barrier()
     except Exception as exc:
         q.put((rank, repr(exc), None, None))
         raise
