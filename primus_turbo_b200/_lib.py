@@ -109,6 +109,8 @@ KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "
 # kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
 _DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")
 _GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k")
+# PTB_NVTX=1: one NVTX range per C-ABI call, named after the entry point (timeline tools show them)
+_NVTX = os.environ.get("PTB_NVTX", "0") not in ("", "0")
 launch_count = 0  # running total of kernels this process enqueued through the C ABI
 _event_log = None  # when a dict: name -> [(start_event, stop_event), ...] on the launching stream
 
@@ -118,6 +120,15 @@ def call(name: str, *args) -> None:
     the current stream (see record_kernel_times), raise PtbError on a non-zero status."""
     global launch_count
     fn = getattr(lib, name)
+    if _NVTX:
+        torch.cuda.nvtx.range_push(name)
+        try:
+            rc = fn(*args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+        check(rc, name)
+        launch_count += KERNELS_PER_CALL.get(name, 1)
+        return
     if _event_log is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()

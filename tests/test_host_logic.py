@@ -148,3 +148,21 @@ def test_quantized_tensor_flatten_unflatten_round_trip():
     assert names == ["_data", "_scale_inv"]
     r = QuantizedTensor.__tensor_unflatten__({n: getattr(plain, n) for n in names}, meta, plain.shape, None)
     assert r.group_lens is None and not r._is_grouped_tensor
+
+
+def test_logger_level_once_and_rank_filters(capsys):
+    """PRIMUS_TURBO_LOG_LEVEL-style logger (primus_turbo/common/logger.py:29-130): once= and rank= filters."""
+    import logging
+
+    from primus_turbo_b200.common import logger
+
+    logger.set_level(logging.INFO)
+    logger.info("hello %d", 1)
+    logger.info("only once", once=True)
+    logger.info("only once", once=True)
+    logger.info("other rank", rank=3)
+    logger.debug("below the level")
+    err = capsys.readouterr().err
+    assert err.count("hello 1") == 1 and err.count("only once") == 1
+    assert "other rank" not in err and "below the level" not in err
+    logger.set_level(logging.WARNING)
