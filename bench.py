@@ -650,7 +650,12 @@ def run_grouped(args):
                 if state["exchange"] is not None:
                     plan = EP.build_peer_plan(counts_here, board or host_group, dev)
                     plan_ms.append((time.perf_counter() - t0) * 1e3)
-                    out = EP.expert_parallel_apply_peer(a_in, local_fn, state["exchange"], plan)
+                    if args.ep_overlap:
+                        # weight quantise beside the dispatch, wgrad beside the return of grad_a
+                        out = EP.ep_grouped_gemm_fp8_peer(a_in, weight, state["exchange"], plan, config=qcfg, overlap=True,
+                                                          reserve_sms=args.ep_reserve_sms)
+                    else:
+                        out = EP.expert_parallel_apply_peer(a_in, local_fn, state["exchange"], plan)
                 else:
                     plan = EP.build_exchange_plan(counts_dev, counts_host=counts_here, host_group=board or host_group)
                     plan_ms.append((time.perf_counter() - t0) * 1e3)
@@ -756,6 +761,7 @@ def run_grouped(args):
         wl = _workload_config(args.config)
         wl.update({"experts": E, "routed_rows": ROWS, "experts_per_gpu": e_loc, "parallelism": f"ep{world}",
                    "exchange": (args.exchange if world > 1 else None), "placement": (args.placement if world > 1 else None),
+                   "ep_overlap": (bool(args.ep_overlap) if world > 1 else None),
                    "load_imbalance_max_over_mean_rows": imbalance,
                    "load_imbalance_contiguous_placement": imbalance_contiguous,
                    "tile_padding_rows_over_rows": pad0 / max(rows0, 1),
@@ -816,6 +822,10 @@ def main():
                     help="N > 1: experts assigned to ranks by greedy balancing of the expected load, or expert e on "
                          "rank e // (E/N)")
     ap.add_argument("--copy-ctas", type=int, default=0, help="CTAs of the peer copy kernel (0: one per SM)")
+    ap.add_argument("--ep-overlap", type=int, default=0,
+                    help="N > 1, peer exchange: 1 = weight quantise beside the dispatch and wgrad beside the return of "
+                         "grad_a on a second stream (give --copy-ctas the same small number as --ep-reserve-sms)")
+    ap.add_argument("--ep-reserve-sms", type=int, default=16, help="SMs wgrad leaves to the overlapped copy kernel")
     ap.add_argument("--bind-cpus", type=int, default=0,
                     help="N > 1: 1 = pin each rank to the CPU cores NVML reports as local to its GPU")
     ap.add_argument("--experts", type=int, default=0, help="smaller case of the same workload (profiling)")

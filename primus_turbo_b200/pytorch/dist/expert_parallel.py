@@ -25,7 +25,8 @@ import torch.distributed as dist
 
 __all__ = [
     "ExchangePlan", "build_exchange_plan", "expert_parallel_apply", "ep_grouped_gemm_fp8", "BlockwiseLocalSteps",
-    "SharedCountsBoard", "PeerPlan", "build_peer_plan", "expert_parallel_apply_peer", "balanced_expert_order",
+    "SharedCountsBoard", "PeerPlan", "build_peer_plan", "expert_parallel_apply_peer", "ep_grouped_gemm_fp8_peer",
+    "balanced_expert_order",
     "load_imbalance",
 ]
 
@@ -314,8 +315,11 @@ class BlockwiseLocalSteps:
         return _get_fp8_dtype(self.config.format, fwd)
 
     def quant_weight(self, w):
+        from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
         from primus_turbo_b200.pytorch.kernels.quantization_impl import quant_fp8_blockwise_for_weight_impl
 
+        if isinstance(w, QuantizedTensor):  # quantised ahead of time (create_quantized_weight)
+            return w.qdata, w.scale_inv
         return quant_fp8_blockwise_for_weight_impl(w, self._dt(True), 128)
 
     def quant_rows(self, x, lens, offs, fwd: bool):
@@ -541,6 +545,76 @@ def expert_parallel_apply_peer(x_local: torch.Tensor, local_fn: Callable[[torch.
     rows = peer_dispatch(x_local, exchange, plan.tables, plan.seg_dev)
     y = local_fn(rows, plan.group_lens)
     return peer_combine(y, exchange, plan.tables, plan.seg_dev)
+
+
+class _EPPeerOverlapped(torch.autograd.Function):
+    """Dispatch -> blockwise grouped GEMM -> combine over the peer-memory exchange as ONE autograd node, so
+    that the two local steps that need nothing from an exchange run beside it on a second stream: the
+    weight quantisation beside the forward dispatch (copy kernel + ordering collective), and wgrad beside
+    the return of the activation gradient.  The copy kernel is launched with few CTAs (``exchange.num_ctas``,
+    it is NVLink-bound) and the persistent wgrad kernel on the SMs that remain (``reserve_sms``), so both are
+    resident together.  Results are bit-identical to the serial form."""
+
+    @staticmethod
+    def forward(ctx, x_local, w_local, plan, exchange, steps, reserve_sms):
+        t = plan.tables
+        fork = _Fork(x_local)
+        fork.begin()
+        with fork.stream():
+            b8, b_s = steps.quant_weight(w_local)
+        rows = exchange.push(x_local.contiguous(), plan.seg_dev[0], "dispatch", t.rows_out)
+        exchange.order()
+        lens = plan.group_lens
+        offs = steps.offsets(lens)
+        a_row, a_col, a_s_row, a_s_col, _, _ = steps.quant_rows(rows, lens, offs, True)
+        fork.join(b8, b_s)
+        y = steps.fwd(a_row, a_s_row, b8, b_s, lens, offs)
+        out = exchange.push(y, plan.seg_dev[1], "combine", t.rows_in)
+        exchange.order()
+        ctx.save_for_backward(a_col, a_s_col, b8, b_s, lens, offs)
+        ctx.plan, ctx.exchange, ctx.steps, ctx.reserve_sms = plan, exchange, steps, reserve_sms
+        return out.clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        a_col, a_s_col, b8, b_s, lens, offs = ctx.saved_tensors
+        plan, exchange, steps = ctx.plan, ctx.exchange, ctx.steps
+        t = plan.tables
+        gy = exchange.push(g.contiguous(), plan.seg_dev[0], "dispatch", t.rows_out, phase="bwd")
+        exchange.order()
+        g_row, g_col, g_s_row, g_s_col, vk_lens, vk_offs = steps.quant_rows(gy, lens, offs, False)
+        ga = steps.dgrad(g_row, g_s_row, b8, b_s, lens, offs)
+        fork = _Fork(g)
+        fork.begin()
+        num_cu = None
+        if fork.cuda and ctx.reserve_sms > 0:
+            num_cu = max(1, torch.cuda.get_device_properties(g.device).multi_processor_count - ctx.reserve_sms)
+        gx = exchange.push(ga, plan.seg_dev[1], "combine", t.rows_in, phase="bwd")  # few CTAs: launched first
+        with fork.stream():
+            fork.uses(a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs)
+            gw = steps.wgrad(a_col, a_s_col, g_col, g_s_col, vk_lens, vk_offs, num_cu)
+        exchange.order()
+        gx = gx.clone()
+        fork.join(gw)
+        return gx, gw, None, None, None, None
+
+
+def ep_grouped_gemm_fp8_peer(x_local: torch.Tensor, w_local: torch.Tensor, exchange, plan: "PeerPlan", trans_b: bool = True,
+                             config=None, overlap: bool = False, reserve_sms: int = 16, steps=None) -> torch.Tensor:
+    """Expert-parallel blockwise ``grouped_gemm_fp8`` over the peer-memory exchange.  ``overlap=True`` runs the
+    weight quantisation beside the dispatch and wgrad beside the return of the activation gradient (give the
+    exchange a small ``num_ctas``, e.g. ``reserve_sms``, so that both kernels of a pair fit on the GPU)."""
+    from primus_turbo_b200.pytorch.ops.grouped_gemm_fp8 import grouped_gemm_fp8
+
+    if not overlap:
+        return expert_parallel_apply_peer(
+            x_local, lambda rows, lens: grouped_gemm_fp8(rows, w_local, lens, trans_b=trans_b, config=config), exchange, plan)
+    if steps is None:
+        from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig
+
+        cfg = config if config is not None else Float8QuantConfig()
+        steps = BlockwiseLocalSteps(cfg, trans_b, torch.promote_types(x_local.dtype, w_local.dtype))
+    return _EPPeerOverlapped.apply(x_local, w_local, plan, exchange, steps, reserve_sms)
 
 
 def balanced_expert_order(expected_load: torch.Tensor, world: int) -> torch.Tensor:

@@ -180,3 +180,101 @@ def test_peer_exchange_forward_backward_two_steps(WORLD, E):
             y, gx = results[r][step]
             assert torch.equal(torch.tensor(y, dtype=torch.float64).reshape(-1, H), y_ref.detach())
             assert torch.equal(torch.tensor(gx, dtype=torch.float64).reshape(-1, H), x.grad)
+
+
+# ---- the single autograd node that overlaps weight quantisation / wgrad with the exchanges ---------------
+def _w(seed, E):
+    g = torch.Generator().manual_seed(100 + seed)
+    return torch.randn(E, 4, H, generator=g, dtype=torch.float64)
+
+
+def _worker_overlapped(rank, store_path, seed, out_q, WORLD, E):
+    from tests.test_expert_parallel_gloo import _TorchSteps
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    torch.multiprocessing.set_sharing_strategy("file_system")
+    dist.init_process_group("gloo", store=dist.FileStore(store_path, WORLD), rank=rank, world_size=WORLD)
+    try:
+        import pickle
+        from multiprocessing.reduction import ForkingPickler
+
+        from primus_turbo_b200.pytorch.dist.expert_parallel import build_peer_plan, ep_grouped_gemm_fp8_peer
+        from primus_turbo_b200.pytorch.dist.peer_exchange import PeerExchange
+
+        regions = {}
+
+        def copy(src, dst_ptrs, segs, row_bytes, num_ctas):
+            flat = src.contiguous().view(torch.uint8).view(src.shape[0], row_bytes)
+            _copy_loop(flat, [regions[p].view(-1, row_bytes) for p in dst_ptrs], segs)
+
+        ex = PeerExchange(None, None, "cpu", capacity_rows=7 * E * WORLD, local_rows=7 * E, copy_fn=copy,
+                          alloc_fn=lambda n: torch.zeros(n, dtype=torch.uint8).share_memory_(),
+                          export_fn=lambda t: bytes(ForkingPickler.dumps(t)), import_fn=pickle.loads)
+        orig_region = ex._region
+
+        def region(direction, row_bytes, phase="fwd"):
+            out = orig_region(direction, row_bytes, phase)
+            for t in out[1]:
+                regions[t.data_ptr()] = t
+            return out
+
+        ex._region = region
+        counts, xs = _routing(seed, WORLD, E)
+        e_loc = E // WORLD
+        x = xs[rank].clone().requires_grad_(True)
+        w = _w(seed, E)[rank * e_loc : (rank + 1) * e_loc].clone().requires_grad_(True)
+        plan = build_peer_plan(counts[rank], dist.group.WORLD, "cpu")
+        y = ep_grouped_gemm_fp8_peer(x, w, ex, plan, overlap=True, steps=_TorchSteps())
+        coeff = torch.arange(y.numel(), dtype=torch.float64).view_as(y) * 1e-2 + 1.0
+        (y * coeff).sum().backward()
+        out_q.put((rank, y.detach().tolist(), x.grad.tolist(), w.grad.tolist()))
+        dist.barrier()
+        ex.close()
+    except Exception as exc:
+        out_q.put((rank, repr(exc), None, None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("WORLD,E", SHAPES)
+def test_peer_exchange_overlapped_node(WORLD, E):
+    from tests.test_expert_parallel_gloo import N_OUT
+
+    seed = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_worker_overlapped, args=(r, os.path.join(d, "store"), seed, q, WORLD, E)) for r in range(WORLD)]
+        for p in procs:
+            p.start()
+        results = {}
+        for _ in range(WORLD):
+            r, y, gx, gw = q.get(timeout=180)
+            assert gx is not None, f"rank {r} failed: {y}"
+            results[r] = (torch.tensor(y, dtype=torch.float64).reshape(-1, N_OUT),
+                          torch.tensor(gx, dtype=torch.float64).reshape(-1, H),
+                          torch.tensor(gw, dtype=torch.float64).reshape(-1, N_OUT, H))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    counts, xs = _routing(seed, WORLD, E)
+    w_full = _w(seed, E).clone().requires_grad_(True)
+    x_all, y_all = [], []
+    for r in range(WORLD):
+        x = xs[r].clone().requires_grad_(True)
+        outs, start = [], 0
+        for e in range(E):
+            n = int(counts[r, e])
+            outs.append(x[start : start + n] @ w_full[e].t())
+            start += n
+        y_ref = torch.cat(outs)
+        coeff = torch.arange(y_ref.numel(), dtype=torch.float64).view_as(y_ref) * 1e-2 + 1.0
+        x_all.append(x)
+        y_all.append((y_ref, coeff))
+    sum((y * c).sum() for y, c in y_all).backward()
+    e_loc = E // WORLD
+    for r in range(WORLD):
+        assert torch.allclose(results[r][0], y_all[r][0].detach(), rtol=0, atol=1e-12)
+        assert torch.allclose(results[r][1], x_all[r].grad, rtol=0, atol=1e-12)
+        assert torch.allclose(results[r][2], w_full.grad[r * e_loc : (r + 1) * e_loc], rtol=0, atol=1e-12)
