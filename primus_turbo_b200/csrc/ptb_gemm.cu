@@ -66,8 +66,6 @@ struct GemmArgs {
     int kind;
     int a_mn, b_mn; // 1: operand stored with the contraction axis strided (MN-major)
     uint32_t idesc;
-    uint32_t idesc_swap; // operand roles exchanged (weights on the MMA M axis), N field left zero
-    int swap_max;        // grouped-rows tiles with at most this many valid rows run with exchanged roles (0: never)
     int M, N, K, G;
     int bn; // tile width the kernel was instantiated with
     int deep; // 1: four-stage variant without output staging
@@ -220,7 +218,6 @@ struct Tile {
     int k_row0;    // first contraction row (variable-K) else 0
     int num_kb;    // 128-wide contraction blocks
     int k_tail;    // variable-K only: valid rows of the last block when the group length is not a multiple of 128, else 0
-    int swap_n;    // 0, or the tile's valid rows rounded up to 16: the tile runs with operand roles exchanged
 };
 
 struct __align__(16) SharedCtl {
@@ -287,7 +284,7 @@ struct Schedule {
             const int nt = rows == 8 ? (p1 >> 3) : p1 / rows;
             const int mt = 8 * p0 + (p1 - nt * rows);
             o.m0 = mt * BM; o.m_end = a.M; o.n0 = nt * a.bn; o.g = 0; o.k_row0 = 0;
-            o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0; o.swap_n = 0;
+            o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
             p1 += step;
         } else if (a.kind == kKindGroupedRows) {
             const int *tile_prefix = ctl->tile_prefix;
@@ -296,11 +293,6 @@ struct Schedule {
             const int lo = offs[g], hi = offs[g + 1];
             o.m0 = lo + (p0 - tile_prefix[g]) * BM; o.m_end = hi; o.n0 = p1 * a.bn; o.g = g;
             o.k_row0 = 0; o.num_kb = (a.K + BK - 1) / BK; o.k_tail = 0;
-            // A group's last tile usually holds far fewer than 128 rows, yet an M = 128 MMA costs the same
-            // whatever its rows hold.  With the operand roles exchanged the rows sit on the MMA's N axis,
-            // which steps in 16s, and the tile costs in proportion to the rows it has.
-            const int valid = hi - o.m0;
-            o.swap_n = (valid <= a.swap_max) ? ((valid + 15) & ~15) : 0;
             p1 += ctl->sched_rem;
             p0 += ctl->sched_q;
             if (p1 >= a.tiles_n) { p1 -= a.tiles_n; ++p0; }
@@ -309,7 +301,6 @@ struct Schedule {
             o.m0 = p1 * BM; o.m_end = a.M; o.n0 = p2 * a.bn; o.g = p0; o.k_row0 = lo;
             o.num_kb = (hi - lo + BK - 1) / BK;
             o.k_tail = (hi - lo) % BK;
-            o.swap_n = 0;
             p2 += ctl->sched_rem;
             p1 += ctl->sched_q;
             if (p2 >= a.tiles_n) { p2 -= a.tiles_n; ++p1; }
@@ -530,29 +521,13 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     if (lane == 0) {
                         const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kABytes;
                         const uint32_t d  = tmem_base + buf * BN;
-                        if (SCALE == kScaleBlock2D && t.swap_n != 0) {
-                            // roles exchanged: each 128-row half of the weight tile is the M operand (K-major
-                            // rows, or one 128-column chunk of an MN-major tile: 16 KiB either way), the token
-                            // tile the N operand with N = the tile's rows rounded up to 16
-                            const uint32_t idesc = args.idesc_swap | ((uint32_t) (t.swap_n >> 3) << 17);
-                            const uint64_t td    = make_smem_desc(sa, 0, 1024);
+                        const uint64_t ad = make_smem_desc(sa, a_lbo, a_sbo);
+                        const uint64_t bd = make_smem_desc(sb, b_lbo, b_sbo);
 #pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const uint64_t wd = make_smem_desc(sb + h * 16384, 0, 1024);
-#pragma unroll
-                                for (int j = 0; j < BK / 32; ++j)
-                                    tc_mma_f8(d + h * 128, wd + (uint64_t) ((b_step * j) >> 4), td + (uint64_t) ((32u * j) >> 4),
-                                              idesc, j > 0 ? 1u : 0u);
-                            }
-                        } else {
-                            const uint64_t ad = make_smem_desc(sa, a_lbo, a_sbo);
-                            const uint64_t bd = make_smem_desc(sb, b_lbo, b_sbo);
-#pragma unroll
-                            for (int j = 0; j < BK / 32; ++j) {
-                                const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
-                                tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
-                                          args.idesc, accumulate);
-                            }
+                        for (int j = 0; j < BK / 32; ++j) {
+                            const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
+                            tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
+                                      args.idesc, accumulate);
                         }
                         tc_commit(smem_u32(&ctl->empty[s])); // stage reusable once these MMAs retire
                     }
@@ -601,33 +576,6 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 cp_async_wait_all(); // nothing of this warp's is in flight when the CTA tears down
                 if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
             }
-            if constexpr (SCALE == kScaleBlock2D) {
-                // Tiles that run with exchanged roles need the token scales per COLUMN of the partial
-                // product: 128 floats per contraction block, staged here for the promotion warps.
-                if (args.swap_max > 0) {
-                    Schedule sched(args, ctl);
-                    Tile t;
-                    uint32_t it = 0;
-                    bool ok     = true;
-                    while (ok && sched.get(t)) {
-                        if (t.swap_n == 0) continue;
-                        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-                            const int slot = it % kScaleSlots;
-                            if (!mbar_wait(smem_u32(&ctl->sc_empty[slot]), ((it / kScaleSlots) & 1) ^ 1)) { ok = false; break; }
-                            float *dst         = &ctl->scale_ring[slot * kSlotFloats];
-                            const float *a_src = args.a_scale + (int64_t) kb * args.as_k;
-#pragma unroll
-                            for (int i = 0; i < BM / 32; ++i) {
-                                const int r = min(t.m0 + i * 32 + lane, t.m_end - 1);
-                                cp_async_f32(dst + i * 32 + lane, a_src + (int64_t) r * args.as_m);
-                            }
-                            cp_async_arrive_on(smem_u32(&ctl->sc_full[slot]));
-                        }
-                    }
-                    cp_async_wait_all();
-                    if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
-                }
-            }
         }
     } else {
         if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -652,7 +600,6 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         Schedule sched(args, ctl);
         Tile t;
         uint32_t acc_it = 0;
-        uint32_t sw_it  = 0; // contraction blocks of exchanged-role tiles so far (position in the scale ring)
         bool ok         = true;
         const bool vec_store = ((args.ldc * sizeof(OutT)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(args.c) & 15u) == 0) &&
                                ((args.c_group_stride * sizeof(OutT)) % 16 == 0);
@@ -668,59 +615,6 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
             const int segs    = kPerBlock ? t.num_kb : (t.num_kb > 0 ? 1 : 0);
 #pragma unroll
             for (int j = 0; j < kWgCols; ++j) acc[j] = 0.0f;
-
-            if constexpr (SCALE == kScaleBlock2D) {
-                if (t.swap_n != 0) {
-                    // ---- tile computed with exchanged roles: TMEM lanes are output COLUMNS (this thread owns
-                    // column col0 + quad*32 + lane), TMEM columns are the tile's rows.  Same arithmetic per
-                    // element as the regular path: acc += partial * (a_scale * b_scale), so a row gets the
-                    // same bits whichever kind of tile it lands in.
-                    const int n_col   = col0 + quad * 32 + lane;
-                    const float *b_sw = args.b_scale + (int64_t) gb * args.bs_g +
-                                        (int64_t) min(col0 / 128, (args.N - 1) / 128) * args.bs_n;
-                    for (int kb = 0; kb < t.num_kb; ++kb, ++acc_it, ++sw_it) {
-                        const uint32_t buf = acc_it % kAccBufs;
-                        const int slot     = sw_it % kScaleSlots;
-                        if (!mbar_wait(smem_u32(&ctl->sc_full[slot]), (sw_it / kScaleSlots) & 1)) { ok = false; break; }
-                        const float *sl = &ctl->scale_ring[slot * kSlotFloats]; // the 128 row scales of this block
-                        const float sbv = b_sw[(int64_t) kb * args.bs_k];
-                        if (!mbar_wait(smem_u32(&ctl->tmem_full[buf]), (acc_it / kAccBufs) & 1)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint32_t taddr = tmem_base + ((uint32_t) (quad * 32) << 16) + buf * BN + wg * kWgCols;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            if (16 * c < t.swap_n) {
-                                float v[16];
-                                tc_ld16(taddr + 16 * c, v);
-                                tc_wait_ld();
-#pragma unroll
-                                for (int j = 0; j < 16; j += 4) {
-                                    const float4 s4 = *reinterpret_cast<const float4 *>(sl + 16 * c + j);
-                                    acc[16 * c + j]     = __fmaf_rn(v[j], s4.x * sbv, acc[16 * c + j]);
-                                    acc[16 * c + j + 1] = __fmaf_rn(v[j + 1], s4.y * sbv, acc[16 * c + j + 1]);
-                                    acc[16 * c + j + 2] = __fmaf_rn(v[j + 2], s4.z * sbv, acc[16 * c + j + 2]);
-                                    acc[16 * c + j + 3] = __fmaf_rn(v[j + 3], s4.w * sbv, acc[16 * c + j + 3]);
-                                }
-                            }
-                        }
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
-                            mbar_arrive(smem_u32(&ctl->sc_empty[slot]));
-                        }
-                    }
-                    if (!ok) break;
-                    if (n_col < args.N) {
-                        OutT *cp        = cbase + (int64_t) t.m0 * args.ldc + n_col;
-                        const int valid = t.m_end - t.m0;
-#pragma unroll
-                        for (int j = 0; j < 128; ++j)
-                            if (j < valid) cp[(int64_t) j * args.ldc] = from_f32<OutT>(acc[j]);
-                    }
-                    continue;
-                }
-            }
 
             // 1-D x 2-D block scales: each thread fetches its two scalars two contraction blocks
             // ahead of their use
@@ -1012,12 +906,6 @@ int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cuda
 }
 
 constexpr int kTileN = 256;
-// Build-time knob for A/B measurements: grouped-rows tiles with at most this many valid rows run with the
-// operand roles exchanged (0 switches the path off).
-#ifndef PTB_SWAP_MAX_ROWS
-#define PTB_SWAP_MAX_ROWS 0
-#endif
-constexpr int kSwapMaxRows = PTB_SWAP_MAX_ROWS;
 
 int scale_mode_of(int granularity, int b_block_2d, int *mode) {
     switch (granularity) {
@@ -1122,9 +1010,6 @@ int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b,
     if (rc) return rc;
     g.kind = kKindGroupedRows; g.a_mn = 0; g.b_mn = trans_b ? 0 : 1;
     g.idesc = make_idesc(a_dtype, b_dtype, g.a_mn, g.b_mn, BN);
-    // exchanged roles for short tail tiles (1-D x 2-D block scales only): weights become the M operand
-    g.idesc_swap = make_idesc(b_dtype, a_dtype, g.b_mn, 0, 0);
-    g.swap_max   = (mode == kScaleBlock2D) ? kSwapMaxRows : 0;
     g.M = (int) M_total; g.N = (int) N; g.K = (int) K; g.G = (int) G;
     g.tiles_n = (int) cdiv<int64_t>(N, BN);
     g.group_offs = group_offs;

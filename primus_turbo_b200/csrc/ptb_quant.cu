@@ -743,11 +743,63 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
     }
 }
 
+// Vector form: one thread dequantises 16 consecutive elements of a row (one 16-byte load of FP8, 32 or 64
+// bytes of output), the row / column split is done once per vector instead of once per element, and the
+// scale is either one value for the whole vector (column blocks of 16 or more) or 16 consecutive
+// values (one scale per column).  Used whenever N is a multiple of 16 and the buffers are aligned.
+template <typename TO, int FMT, bool PER_COLUMN>
+__global__ void __launch_bounds__(256) dequant_vec_kernel(const uint8_t *__restrict__ q, int64_t nvec,
+                                                           const float *__restrict__ scale_inv, DequantIdx ix,
+                                                           TO *__restrict__ out) {
+    const int64_t vec_per_row = ix.N / 16;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t rw = i / vec_per_row, col = (i - rw * vec_per_row) * 16;
+        const int64_t m = rw % ix.M, b = rw / ix.M;
+        const int64_t si = b * ix.sb + (m / ix.bm) * ix.sm + (col / ix.bn) * ix.sn;
+        const uint4 raw  = *reinterpret_cast<const uint4 *>(q + i * 16);
+        const uint8_t *e = reinterpret_cast<const uint8_t *>(&raw);
+        float sc[16];
+        if constexpr (PER_COLUMN) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(scale_inv + si + 4 * k);
+                sc[4 * k] = s4.x; sc[4 * k + 1] = s4.y; sc[4 * k + 2] = s4.z; sc[4 * k + 3] = s4.w;
+            }
+        } else {
+            const float s1 = scale_inv[si];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) sc[k] = s1;
+        }
+        TO o[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) o[k] = from_f32<TO>(fp8_to_f32<FMT>(e[k]) * sc[k]);
+        uint4 *dst = reinterpret_cast<uint4 *>(out + i * 16);
+#pragma unroll
+        for (int k = 0; k < (int) (sizeof(TO) * 16 / 16); ++k) dst[k] = reinterpret_cast<const uint4 *>(o)[k];
+    }
+}
+
 int launch_dequant(const void *q, int q_dtype, int64_t n, const float *s, const DequantIdx &ix, void *out,
                    int out_dtype, cudaStream_t st) {
     if (n == 0) return 0;
     PTB_REQUIRE(q && s && out, PTB_ERR_ARG, "dequant: null pointer");
     PTB_REQUIRE(is_hp(out_dtype) && is_fp8(q_dtype), PTB_ERR_ARG, "dequant: bad dtype");
+    const bool per_column = ix.bn == 1 && ix.sn == 1;
+    const bool one_scale  = ix.sn == 0 || (ix.bn >= 16 && ix.bn % 16 == 0);
+    if (ix.N % 16 == 0 && (per_column || one_scale) && aligned16(q) && aligned16(out) &&
+        (!per_column || (aligned16(s) && ix.sb % 4 == 0 && ix.sm % 4 == 0))) {
+        const int64_t nvec = n / 16;
+        const int blocks   = (int) imin(cdiv<int64_t>(nvec, 256), 148 * 32);
+        if (per_column) {
+            PTB_SWITCH_HP(out_dtype, TO, PTB_SWITCH_FP8(q_dtype, FMT,
+                (dequant_vec_kernel<TO, FMT, true><<<blocks, 256, 0, st>>>((const uint8_t *) q, nvec, s, ix, (TO *) out))));
+        } else {
+            PTB_SWITCH_HP(out_dtype, TO, PTB_SWITCH_FP8(q_dtype, FMT,
+                (dequant_vec_kernel<TO, FMT, false><<<blocks, 256, 0, st>>>((const uint8_t *) q, nvec, s, ix, (TO *) out))));
+        }
+        PTB_LAUNCH_CHECK("dequant_vec_kernel");
+        return 0;
+    }
     const int blocks = (int) imin(cdiv<int64_t>(n, 256), 148 * 16);
     PTB_SWITCH_HP(out_dtype, TO, PTB_SWITCH_FP8(q_dtype, FMT,
         (dequant_kernel<TO, FMT><<<blocks, 256, 0, st>>>((const uint8_t *) q, n, s, ix, (TO *) out))));
@@ -1036,6 +1088,11 @@ int ptb_dequant_fp8_rowwise(const void *q, int q_dtype, int64_t B, int64_t M, in
                             void *out, int out_dtype, ptb_stream_t stream) {
     PTB_REQUIRE(B >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "dequant_rowwise: negative size");
     if (B * M * N == 0) return 0;
+    if (N == 1) {
+        // the scaled axis is the innermost one: B rows of M elements, one scale per row
+        DequantIdx rows{B, M, 0, 1, 1, INT64_MAX, 0}; // scale[m]
+        return launch_dequant(q, q_dtype, B * M, scale_inv, rows, out, out_dtype, (cudaStream_t) stream);
+    }
     DequantIdx ix{M, N, N, INT64_MAX, 0, 1, 1}; // scale[b, 0, n]
     return launch_dequant(q, q_dtype, B * M * N, scale_inv, ix, out, out_dtype, (cudaStream_t) stream);
 }
