@@ -273,6 +273,39 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
                  int64_t a_scale_stride_k, const float *b_scale, int64_t b_scale_stride_n,
                  int64_t b_scale_stride_k, int b_block_2d, int num_sms, ptb_stream_t stream);
 
+/* ------------------------------------------------------------------ MXFP8 (1x32 blocks, E8M0 scales) */
+/* Quantise x[G][M][N] (bf16/fp16, contiguous; G = 1 for a matrix) in one pass into
+ *   q_row[G][M][N_pad]  + s_row[G][M][N_pad/32]   blocks of 32 along a row,
+ *   q_col[G][N][M_pad]  + s_col[G][N][M_pad/32]   blocks of 32 along a column, stored TRANSPOSED,
+ * N_pad / M_pad = N / M rounded up to 128; the padding holds zero bytes with scale byte 0.  A scale byte
+ * is a biased power-of-two exponent (E8M0).  Either direction may be omitted (both its pointers NULL).
+ * row_2d_block / col_2d_block != 0: one scale per 32x32 tile for that direction.  N % 32 == 0; x and
+ * the FP8 outputs 16-byte aligned.
+ * Replaces the torch ops quantize_mxfp8 / quantize_mxfp8_dual
+ * (csrc/pytorch/quantization/quantization.cpp:736-966, kernels csrc/kernels/quantization/quantization_mxfp8.cu);
+ * the reference's shuffled layouts (scale or data pre-shuffle for its own GEMM back ends) are not offered. */
+int ptb_quant_mxfp8(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, void *q_row, void *s_row,
+                    void *q_col, void *s_col, int row_2d_block, int col_2d_block, int q_dtype,
+                    ptb_stream_t stream);
+
+/* out = cast(float(q[R][C]) * 2^(scale byte - 127)) (byte 0 multiplies by 0.0f as the reference does),
+ * scales[R][C/32]; transpose_out != 0 writes out[C][R] (the column-direction data come back as
+ * [M_pad][N]).  Replaces dequantize_mxfp8 (quantization.cpp:283-358, dequantization_mxfp8.cu:47-100). */
+int ptb_dequant_mxfp8(const void *q, int q_dtype, int64_t R, int64_t C, const void *scales,
+                      int transpose_out, void *out, int out_dtype, ptb_stream_t stream);
+
+/* C[M,N] = A[M,K] . B[N,K]^T with one E8M0 scale per 32 contraction elements of every A and B row,
+ * applied by the block-scaled tensor-core instruction (tcgen05.mma kind::mxf8f6f4.block_scale); fp32
+ * accumulation over the whole K, c_dtype output.  K is the padded extent (a multiple of 128);
+ * a_sf[M][a_sf_ld], b_sf[N][b_sf_ld] bytes with a_sf_ld, b_sf_ld >= K/32, multiples of 4, 4-byte
+ * aligned bases.  Every MX GEMM of the reference is this NT form (forward, dgrad and wgrad use the
+ * row- and column-direction copies: primus_turbo/pytorch/ops/gemm_fp8.py:582-640).  Replaces
+ * gemm_fp8_impl with granularity MX_BLOCKWISE (kernels/gemm/gemm_fp8_impl.py:438-467). */
+int ptb_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, int64_t a_sf_ld,
+                   const void *b, int b_dtype, int64_t ldb, const void *b_sf, int64_t b_sf_ld, void *c,
+                   int c_dtype, int64_t ldc, int64_t M, int64_t N, int64_t K, int num_sms,
+                   ptb_stream_t stream);
+
 /* Grouped GEMM over row segments of a (forward and dgrad of the MoE experts):
  *   out[offs[g]:offs[g+1], :] = a[offs[g]:offs[g+1], :] . op(b[g]),   rows >= offs[G] zeroed.
  *   a [M_total, K]; b [G, N, K] (trans_b = 1) or [G, K, N] (trans_b = 0), contiguous;

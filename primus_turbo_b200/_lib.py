@@ -63,6 +63,9 @@ _PROTOS = {
     "ptb_gather_rows_scaled": [_P, _I, _P, _P, _L, _L, _L, _P, _P],
     "ptb_unpermute_rows": [_P, _I, _P, _P, _L, _L, _L, _P, _P],
     "ptb_unpermute_rows_bwd": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P, _P],
+    "ptb_quant_mxfp8": [_P, _I, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ptb_dequant_mxfp8": [_P, _I, _L, _L, _P, _I, _P, _I, _P],
+    "ptb_gemm_mxfp8": [_P, _I, _L, _P, _L, _P, _I, _L, _P, _L, _P, _I, _L, _L, _L, _L, _I, _P],
     "ptb_gemm_status": [ctypes.POINTER(c_int), _I],
     "ptb_gemm_wait_selftest": [_P],
 }
@@ -108,7 +111,7 @@ KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "
 # PTB_DEBUG_STATUS=1: after every GEMM call, wait for the device and raise if a bounded wait inside the
 # kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
 _DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")
-_GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k")
+_GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_gemm_mxfp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k")
 # PTB_NVTX=1: one NVTX range per C-ABI call, named after the entry point (timeline tools show them)
 _NVTX = os.environ.get("PTB_NVTX", "0") not in ("", "0")
 launch_count = 0  # running total of kernels this process enqueued through the C ABI

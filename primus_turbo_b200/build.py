@@ -18,7 +18,7 @@ CSRC = PKG_DIR / "csrc"
 OUT_DIR = PKG_DIR / "_C"
 LIB_PATH = OUT_DIR / "libptb_b200.so"
 
-SOURCES = ["ptb_quant.cu", "ptb_gemm.cu", "ptb_exchange.cu", "ptb_activation.cu"]
+SOURCES = ["ptb_quant.cu", "ptb_gemm.cu", "ptb_exchange.cu", "ptb_activation.cu", "ptb_mxfp8.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -52,7 +52,11 @@ constexpr int kSlotFloats = 128 + 256;
 constexpr int kMaxGroups  = 1024;                 // tile table entries kept in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
 
-constexpr int kScaleTensor = 0, kScaleRow = 1, kScaleBlock2D = 2, kScaleBlock1D = 3;
+constexpr int kScaleTensor = 0, kScaleRow = 1, kScaleBlock2D = 2, kScaleBlock1D = 3, kScaleMX = 4;
+// MX mode: E8M0 scale bytes, one per 32 contraction elements, travel global -> shared ring -> tensor
+// memory (tcgen05.cp) and are applied by the block-scaled MMA itself; the accumulator then needs
+// no promotion and one 256-column TMEM buffer leaves columns 256.. for the scale factors.
+constexpr int kSfTmemCol0 = 256, kSfTmemColsPerSlot = 16; // per ring slot: 4 columns for A's 128 rows, 8 for B's 256
 constexpr int kKindDense = 0, kKindGroupedRows = 1, kKindGroupedK = 2;
 
 // status word written by a kernel whose wait ran out (0 = never happened)
@@ -77,6 +81,9 @@ struct GemmArgs {
     int64_t as_m, as_k;
     const float *b_scale;
     int64_t bs_g, bs_n, bs_k;
+    // MX mode: scale bytes [rows][K / 32], row pitch in bytes (a multiple of 4)
+    const uint8_t *a_sf, *b_sf;
+    int64_t a_sf_ld, b_sf_ld;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -168,6 +175,19 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
                  "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// block-scaled FP8 MMA: one E8M0 scale per 32 contraction elements of every A row and B row, read from
+// tensor memory; the byte of the 32-bit scale cell to use is part of the instruction descriptor
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::"r"(d_tmem),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+                 : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns of lanes 0-31, repeated in all four lane quarters
+__device__ __forceinline__ void tc_cp_sf(uint32_t dst_tmem, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(sdesc) : "memory");
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
@@ -206,6 +226,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     d |= (uint64_t) ((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (uint64_t) 1 << 46; // descriptor version
     d |= (uint64_t) 2 << 61; // SWIZZLE_128B
+    return d;
+}
+
+// Shared-memory descriptor of a 128-row scale-factor atom for tcgen05.cp: no swizzle, rows of 16 bytes,
+// 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t) (128u >> 4) << 32;
+    d |= (uint64_t) 1 << 46;
     return d;
 }
 
@@ -365,7 +395,7 @@ template <int SCALE, typename OutT, int BN, int DEEP>
 __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(const __grid_constant__ GemmArgs args) {
     using G_ = Geo<BN, DEEP>;
     constexpr int kStages = G_::kStages, kStageBytes = G_::kStageBytes, kThreads = G_::kThreads;
-    constexpr int kAccBufs = G_::kAccBufs, kWgCols = G_::kSliceCols, kChunks = G_::kChunks;
+    constexpr int kAccBufs = (SCALE == kScaleMX) ? 1 : G_::kAccBufs, kWgCols = G_::kSliceCols, kChunks = G_::kChunks;
     constexpr int kCStageBytes = G_::kCStageBytes, kEpiWarps = G_::kEpiWarps;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -389,7 +419,8 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         }
         for (int b = 0; b < kScaleSlots; ++b) {
             mbar_init(smem_u32(&ctl->sc_full[b]), 32);         // every loader lane, after its own copies
-            mbar_init(smem_u32(&ctl->sc_empty[b]), kEpiWarps); // one arrival per promotion warp
+            // one arrival per promotion warp; in MX mode the MMA issuer's commit frees the slot
+            mbar_init(smem_u32(&ctl->sc_empty[b]), SCALE == kScaleMX ? 1 : kEpiWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -502,6 +533,10 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                         if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), ((acc_it / kAccBufs) & 1) ^ 1)) { ok = false; break; }
                     }
                     if (!mbar_wait(smem_u32(&ctl->full[s]), ph)) { ok = false; break; }
+                    const int slot = it % kScaleSlots;
+                    if constexpr (SCALE == kScaleMX) {
+                        if (!mbar_wait(smem_u32(&ctl->sc_full[slot]), (it / kScaleSlots) & 1)) { ok = false; break; }
+                    }
                     uint8_t *a_tile = smem + s * kStageBytes;
                     if (t.k_tail != 0 && kb == t.num_kb - 1) {
                         // The last block of an unpadded group reaches into the next group's rows (or
@@ -523,11 +558,29 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                         const uint32_t d  = tmem_base + buf * BN;
                         const uint64_t ad = make_smem_desc(sa, a_lbo, a_sbo);
                         const uint64_t bd = make_smem_desc(sb, b_lbo, b_sbo);
+                        if constexpr (SCALE == kScaleMX) {
+                            // this block's scale bytes: three 512-byte atoms (A rows, B rows 0-127, B rows 128-255)
+                            const uint32_t sf_smem = smem_u32(&ctl->scale_ring[slot * kSlotFloats]);
+                            const uint32_t sf_tmem = tmem_base + kSfTmemCol0 + slot * kSfTmemColsPerSlot;
+                            tc_cp_sf(sf_tmem, make_sf_desc(sf_smem));
+                            tc_cp_sf(sf_tmem + 4, make_sf_desc(sf_smem + 512));
+                            tc_cp_sf(sf_tmem + 8, make_sf_desc(sf_smem + 1024));
 #pragma unroll
-                        for (int j = 0; j < BK / 32; ++j) {
-                            const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
-                            tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
-                                      args.idesc, accumulate);
+                            for (int j = 0; j < BK / 32; ++j) {
+                                const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
+                                // byte j of each scale cell belongs to the j-th 32-wide slice of the block
+                                const uint32_t idesc = args.idesc | ((uint32_t) j << 29) | ((uint32_t) j << 4);
+                                tc_mma_mxf8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4), idesc,
+                                            sf_tmem, sf_tmem + 4, accumulate);
+                            }
+                            tc_commit(smem_u32(&ctl->sc_empty[slot])); // scale slot reusable once copies and MMAs retire
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BK / 32; ++j) {
+                                const uint32_t accumulate = (j > 0 || !new_acc) ? 1u : 0u;
+                                tc_mma_f8(d, ad + (uint64_t) ((a_step * j) >> 4), bd + (uint64_t) ((b_step * j) >> 4),
+                                          args.idesc, accumulate);
+                            }
                         }
                         tc_commit(smem_u32(&ctl->empty[s])); // stage reusable once these MMAs retire
                     }
@@ -574,6 +627,50 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     }
                 }
                 cp_async_wait_all(); // nothing of this warp's is in flight when the CTA tears down
+                if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
+            }
+            if constexpr (SCALE == kScaleMX) {
+                // Gathers each contraction block's scale bytes -- one aligned 32-bit word (four 32-wide
+                // slices) per operand row -- and lays them out as tcgen05.cp wants them: row r of a 128-row
+                // atom at byte 16 * (r % 32) + 4 * (r / 32), so a lane's four rows (lane, lane + 32, ...)
+                // are one 16-byte store.  The words of the next block are fetched before this block's are
+                // stored, so a global round trip is off the critical path inside a tile.
+                Schedule sched(args, ctl);
+                Tile t;
+                uint32_t it = 0;
+                bool ok     = true;
+                while (ok && sched.get(t)) {
+                    int row[12]; // operand rows whose scale words this lane moves (clamped: rows past the end are never stored)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        row[i]     = min(t.m0 + lane + 32 * i, t.m_end - 1);
+                        row[4 + i] = min(t.n0 + lane + 32 * i, args.N - 1);
+                        row[8 + i] = min(t.n0 + 128 + lane + 32 * i, args.N - 1);
+                    }
+                    auto fetch = [&](int i, int kb) {
+                        const uint8_t *base = i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld : args.b_sf + (int64_t) row[i] * args.b_sf_ld;
+                        return __ldg(reinterpret_cast<const uint32_t *>(base + 4 * kb));
+                    };
+                    uint32_t cur[12], nxt[12];
+#pragma unroll
+                    for (int i = 0; i < 12; ++i) cur[i] = t.num_kb > 0 ? fetch(i, 0) : 0u;
+                    for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+                        if (kb + 1 < t.num_kb) {
+#pragma unroll
+                            for (int i = 0; i < 12; ++i) nxt[i] = fetch(i, kb + 1);
+                        }
+                        const int slot = it % kScaleSlots;
+                        if (!mbar_wait(smem_u32(&ctl->sc_empty[slot]), ((it / kScaleSlots) & 1) ^ 1)) { ok = false; break; }
+                        const uint32_t dst = smem_u32(&ctl->scale_ring[slot * kSlotFloats]) + lane * 16;
+                        st_shared_v4(dst, make_uint4(cur[0], cur[1], cur[2], cur[3]));
+                        st_shared_v4(dst + 512, make_uint4(cur[4], cur[5], cur[6], cur[7]));
+                        st_shared_v4(dst + 1024, make_uint4(cur[8], cur[9], cur[10], cur[11]));
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // tcgen05.cp reads through the async proxy
+                        mbar_arrive(smem_u32(&ctl->sc_full[slot]));
+#pragma unroll
+                        for (int i = 0; i < 12; ++i) cur[i] = nxt[i];
+                    }
+                }
                 if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
             }
         }
@@ -853,6 +950,18 @@ uint32_t make_idesc(int a_dtype, int b_dtype, int a_mn, int b_mn, int BN) {
     return d;
 }
 
+// Block-scaled (MX) descriptor: no accumulator-format field; bits 4-5 and 29-30 select the scale byte
+// of B and A (filled in per instruction), bit 23 says the scales are E8M0.
+uint32_t make_idesc_mx(int a_dtype, int b_dtype, int BN) {
+    uint32_t d = 0;
+    d |= (a_dtype == PTB_E5M2 ? 1u : 0u) << 7;       // A format
+    d |= (b_dtype == PTB_E5M2 ? 1u : 0u) << 10;      // B format
+    d |= (uint32_t) (BN >> 3) << 17;                 // N
+    d |= 1u << 23;                                   // scale format E8M0
+    d |= (uint32_t) (BM >> 4) << 24;                 // M
+    return d;
+}
+
 template <int BN, int DEEP> constexpr size_t smem_bytes() {
     return 1024 + (size_t) Geo<BN, DEEP>::kStages * Geo<BN, DEEP>::kStageBytes + Geo<BN, DEEP>::kCStageBytes +
            sizeof(SharedCtl);
@@ -901,6 +1010,7 @@ int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cuda
     case kScaleRow: return launch_scale<kScaleRow>(args, out_dtype, grid, st);
     case kScaleBlock2D: return launch_scale<kScaleBlock2D>(args, out_dtype, grid, st);
     case kScaleBlock1D: return launch_scale<kScaleBlock1D>(args, out_dtype, grid, st);
+    case kScaleMX: return launch_scale<kScaleMX>(args, out_dtype, grid, st);
     default: return fail(PTB_ERR_ARG, "unknown scale mode %d", scale_mode);
     }
 }
@@ -982,6 +1092,37 @@ int ptb_gemm_fp8(const void *a, int a_dtype, int trans_a, int64_t lda, const voi
     g.a_scale = a_scale; g.as_m = a_scale_stride_m; g.as_k = a_scale_stride_k;
     g.b_scale = b_scale; g.bs_g = 0; g.bs_n = b_scale_stride_n; g.bs_k = b_scale_stride_k;
     return launch_gemm(g, mode, c_dtype, num_sms, (cudaStream_t) stream);
+}
+
+int ptb_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, int64_t a_sf_ld, const void *b, int b_dtype,
+                   int64_t ldb, const void *b_sf, int64_t b_sf_ld, void *c, int c_dtype, int64_t ldc, int64_t M, int64_t N,
+                   int64_t K, int num_sms, ptb_stream_t stream) {
+    PTB_REQUIRE(M >= 0 && N >= 0 && K > 0, PTB_ERR_ARG, "gemm_mxfp8: bad shape M=%lld N=%lld K=%lld", (long long) M,
+                (long long) N, (long long) K);
+    if (M == 0 || N == 0) return 0;
+    PTB_REQUIRE(a && b && c && a_sf && b_sf, PTB_ERR_ARG, "gemm_mxfp8: null pointer");
+    PTB_REQUIRE(is_fp8(a_dtype) && is_fp8(b_dtype), PTB_ERR_ARG, "gemm_mxfp8: operands must be FP8");
+    PTB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), PTB_ERR_TOO_LARGE, "gemm_mxfp8: dimension too large");
+    PTB_REQUIRE(K % BK == 0, PTB_ERR_ARG, "gemm_mxfp8: the (padded) contraction extent %lld must be a multiple of 128", (long long) K);
+    PTB_REQUIRE(a_sf_ld >= K / 32 && b_sf_ld >= K / 32 && a_sf_ld % 4 == 0 && b_sf_ld % 4 == 0 &&
+                    (reinterpret_cast<uintptr_t>(a_sf) & 3u) == 0 && (reinterpret_cast<uintptr_t>(b_sf) & 3u) == 0,
+                PTB_ERR_ALIGN, "gemm_mxfp8: scale rows must hold K/32 bytes, be 4-byte aligned and a multiple of 4 bytes apart");
+    GemmArgs g{};
+    const int BN = kTileN;
+    g.bn         = BN;
+    int rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M, 1, (uint64_t) lda, (uint64_t) lda * M, BM);
+    if (rc) return rc;
+    rc = make_map(&g.tm_b, b, (uint64_t) K, (uint64_t) N, 1, (uint64_t) ldb, (uint64_t) ldb * N, BN);
+    if (rc) return rc;
+    g.kind = kKindDense; g.a_mn = 0; g.b_mn = 0;
+    g.idesc = make_idesc_mx(a_dtype, b_dtype, BN);
+    g.M = (int) M; g.N = (int) N; g.K = (int) K; g.G = 1;
+    g.tiles_n = (int) cdiv<int64_t>(N, BN);
+    g.c = c; g.ldc = ldc; g.c_group_stride = 0;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, c, c_dtype, (uint64_t) N, (uint64_t) M, 1, (uint64_t) ldc, 0);
+    if (rc) return rc;
+    g.a_sf = (const uint8_t *) a_sf; g.a_sf_ld = a_sf_ld; g.b_sf = (const uint8_t *) b_sf; g.b_sf_ld = b_sf_ld;
+    return launch_gemm(g, kScaleMX, c_dtype, num_sms, (cudaStream_t) stream);
 }
 
 int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b, int b_dtype, int trans_b, void *out,

@@ -1,0 +1,267 @@
+// MXFP8 quantise / dequantise for sm_100a: 1x32 (or 32x32) blocks with power-of-two E8M0 scales.
+//
+// Semantics follow the reference's csrc/kernels/quantization/quantization_mxfp8.cu (scale from the block
+// maximum: lines 71-110; 32x32 tiles, zero fill outside the matrix, clamp to +-(fmax * scale) then divide
+// by the scale: lines 128-515) and dequantization_mxfp8.cu:47-100.  Layouts follow
+// csrc/pytorch/quantization/quantization.cpp:736-966: the row-direction output is [M, N_pad], the
+// column-direction output is stored TRANSPOSED as [N, M_pad], padded extents are multiples of 128 and
+// hold zero bytes with scale byte 0, scales are one byte per 32 elements along the padded extent.
+//
+// One pass over the input produces both directions.  A warp owns a 32-row x 64-column tile and never
+// talks to another warp: row maxima reduce over the four lanes of a 32-column block, column maxima over
+// the four lanes that share a column, and the transposed output is assembled with a 4x4 byte transpose
+// across those four lanes, so every lane ends up holding 32 contiguous output bytes of two columns.
+#include "ptb_common.cuh"
+
+namespace ptb {
+namespace {
+
+constexpr int kMxBlock = 32;
+constexpr int kMxPad   = 128;
+
+template <int FMT> struct MxFmt;
+template <> struct MxFmt<PTB_E4M3> { static constexpr int mbits = 3, target_pow2 = 8; };
+template <> struct MxFmt<PTB_E5M2> { static constexpr int mbits = 2, target_pow2 = 15; };
+
+// Block maximum -> biased E8M0 byte.  The maximum's mantissa is rounded to the FP8 format's width (the
+// carry may bump the exponent), the exponent of the format's largest power of two is subtracted, the
+// result is clamped to [-127, 128] and biased by 127.
+template <int FMT> __device__ __forceinline__ int mx_biased_exponent(float amax) {
+    const uint32_t bits = __float_as_uint(amax);
+    const int add       = 1 << (23 - MxFmt<FMT>::mbits - 1);
+    int e               = (int) (((bits + (uint32_t) add) >> 23) & 0x1ffu) - 127 - MxFmt<FMT>::target_pow2;
+    e                   = max(e, -127);
+    e                   = min(e, 128);
+    return e + 127;
+}
+// The clamp limit fmax * (byte << 23 read as fp32) -- byte 0 gives 0.0f, byte 255 gives +inf, as in the
+// reference -- and the exact reciprocal 2^(127 - byte) (subnormal for bytes 254 and 255).
+template <int FMT> __device__ __forceinline__ void mx_limits(int biased, float &lim, float &inv) {
+    lim = __fmul_rn(Fp8Max<FMT>::v, __uint_as_float((uint32_t) biased << 23));
+    const int e = 127 - biased; // 127 .. -128
+    inv         = (e >= -126) ? __uint_as_float((uint32_t) (e + 127) << 23) : __uint_as_float(1u << (149 + e));
+}
+
+struct MxQuantArgs {
+    const void *x;
+    uint8_t *q_row, *s_row, *q_col, *s_col;
+    int64_t M, N, M_pad, N_pad;
+    int row_2d, col_2d;
+};
+
+template <typename T> __device__ __forceinline__ void decode8(const uint4 &raw, float (&v)[8]) {
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(e[i]);
+}
+
+template <int FMT> __device__ __forceinline__ uint32_t mx_cvt4(const float *v, float lim, float inv) {
+    float c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(fminf(fmaxf(v[i], -lim), lim), inv);
+    return (uint32_t) cvt_fp8x2<FMT>(c[0], c[1]) | ((uint32_t) cvt_fp8x2<FMT>(c[2], c[3]) << 16);
+}
+
+// grid: (N_pad / 128, M_pad / 128, G); 256 threads; warp w: rows 32 * (w & 3), columns 64 * (w >> 2)
+template <typename T, int FMT> __global__ void __launch_bounds__(256) mx_quant_kernel(const MxQuantArgs p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rl = lane >> 3, cl = lane & 7;
+    const int64_t g    = blockIdx.z;
+    const int64_t row0 = (int64_t) blockIdx.y * 128 + 32 * (warp & 3);
+    const int64_t col0 = (int64_t) blockIdx.x * 128 + 64 * (warp >> 2);
+    const int64_t col  = col0 + cl * 8;
+    const T *x         = reinterpret_cast<const T *>(p.x) + g * p.M * p.N;
+
+    uint4 raw[8];
+#pragma unroll
+    for (int ps = 0; ps < 8; ++ps) {
+        const int64_t r = row0 + 4 * ps + rl;
+        raw[ps]         = (r < p.M && col < p.N) ? *reinterpret_cast<const uint4 *>(x + r * p.N + col) : make_uint4(0, 0, 0, 0);
+    }
+    float rmax[8], cmax[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cmax[j] = 0.0f;
+#pragma unroll
+    for (int ps = 0; ps < 8; ++ps) {
+        float v[8];
+        decode8<T>(raw[ps], v);
+        float m = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float a = fabsf(v[j]);
+            m             = fmaxf(m, a);
+            cmax[j]       = fmaxf(cmax[j], a);
+        }
+        m        = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        rmax[ps] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2)); // the four lanes of a 32-column block
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        cmax[j] = fmaxf(cmax[j], __shfl_xor_sync(0xffffffffu, cmax[j], 8));
+        cmax[j] = fmaxf(cmax[j], __shfl_xor_sync(0xffffffffu, cmax[j], 16)); // the four lanes that share a column
+    }
+    float tmax = 0.0f; // maximum of the 32x32 tile this lane's columns belong to
+    if (p.row_2d || p.col_2d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tmax = fmaxf(tmax, cmax[j]);
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    }
+
+    // ---- row direction: q_row[g][r][col .. col+7], s_row[g][r][col / 32] -----------------------------
+    if (p.q_row != nullptr) {
+        uint8_t *q       = p.q_row + g * p.M * p.N_pad;
+        uint8_t *s       = p.s_row + g * p.M * (p.N_pad / kMxBlock);
+        const int tile_b = mx_biased_exponent<FMT>(tmax);
+#pragma unroll
+        for (int ps = 0; ps < 8; ++ps) {
+            const int64_t r = row0 + 4 * ps + rl;
+            if (r >= p.M) continue;
+            const int biased = p.row_2d ? tile_b : mx_biased_exponent<FMT>(rmax[ps]);
+            float lim, inv;
+            mx_limits<FMT>(biased, lim, inv);
+            float v[8];
+            decode8<T>(raw[ps], v);
+            *reinterpret_cast<uint2 *>(q + r * p.N_pad + col) = make_uint2(mx_cvt4<FMT>(v, lim, inv), mx_cvt4<FMT>(v + 4, lim, inv));
+            if ((cl & 3) == 0) s[r * (p.N_pad / kMxBlock) + col / kMxBlock] = (uint8_t) biased;
+        }
+    }
+
+    // ---- column direction: q_col[g][c][row0 .. row0+31] (transposed), s_col[g][c][row0 / 32] ---------
+    if (p.q_col != nullptr) {
+        uint8_t *q = p.q_col + g * p.N * p.M_pad;
+        uint8_t *s = p.s_col + g * p.N * (p.M_pad / kMxBlock);
+        float lim[8], inv[8];
+        const int tile_b = mx_biased_exponent<FMT>(tmax);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int biased = p.col_2d ? tile_b : mx_biased_exponent<FMT>(cmax[j]);
+            mx_limits<FMT>(biased, lim[j], inv[j]);
+            if (rl == 0 && col + j < p.N) s[(col + j) * (p.M_pad / kMxBlock) + row0 / kMxBlock] = (uint8_t) biased;
+        }
+        // w[ps][h]: this lane's row (4 ps + rl), columns 4 h .. 4 h + 3, one byte each
+        uint32_t w[8][2];
+#pragma unroll
+        for (int ps = 0; ps < 8; ++ps) {
+            float v[8];
+            decode8<T>(raw[ps], v);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float c[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(fminf(fmaxf(v[4 * h + i], -lim[4 * h + i]), lim[4 * h + i]), inv[4 * h + i]);
+                w[ps][h] = (uint32_t) cvt_fp8x2<FMT>(c[0], c[1]) | ((uint32_t) cvt_fp8x2<FMT>(c[2], c[3]) << 16);
+            }
+        }
+        // 4x4 byte transpose across the lanes rl = 0..3 (lane bits 3 and 4): afterwards byte k of
+        // w[ps][h] is row 4 ps + k of column 4 h + rl
+#pragma unroll
+        for (int ps = 0; ps < 8; ++ps) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t mine  = w[ps][h];
+                uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                mine           = (rl & 1) ? __byte_perm(mine, other, 0x3715) : __byte_perm(mine, other, 0x6240);
+                other          = __shfl_xor_sync(0xffffffffu, mine, 16);
+                mine           = (rl & 2) ? __byte_perm(mine, other, 0x3276) : __byte_perm(mine, other, 0x5410);
+                w[ps][h]       = mine;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t c = col + 4 * h + rl;
+            if (c < p.N) {
+                uint4 *dst = reinterpret_cast<uint4 *>(q + c * p.M_pad + row0);
+                dst[0]     = make_uint4(w[0][h], w[1][h], w[2][h], w[3][h]);
+                dst[1]     = make_uint4(w[4][h], w[5][h], w[6][h], w[7][h]);
+            }
+        }
+    }
+}
+
+// out[r][c] = cast(float(q[r][c]) * (scale byte << 23 read as fp32)); TRANSPOSE writes out[c][r] instead
+template <typename TO, int FMT, bool TRANSPOSE>
+__global__ void __launch_bounds__(256) mx_dequant_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict__ s,
+                                                         int64_t R, int64_t C, TO *__restrict__ out) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+    const int64_t c0 = (int64_t) blockIdx.x * 32, r0 = (int64_t) blockIdx.y * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t r = r0 + ty + 8 * i, c = c0 + tx;
+        float v = 0.0f;
+        if (r < R && c < C) {
+            const float sc = __uint_as_float((uint32_t) s[r * (C / kMxBlock) + c / kMxBlock] << 23);
+            v              = __fmul_rn(fp8_to_f32<FMT>(q[r * C + c]), sc);
+        }
+        if constexpr (TRANSPOSE) tile[ty + 8 * i][tx] = v;
+        else if (r < R && c < C) out[r * C + c] = from_f32<TO>(v);
+    }
+    if constexpr (TRANSPOSE) {
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t c = c0 + ty + 8 * i, r = r0 + tx; // out is [C][R]
+            if (r < R && c < C) out[c * R + r] = from_f32<TO>(tile[tx][ty + 8 * i]);
+        }
+    }
+}
+
+} // namespace
+} // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int ptb_quant_mxfp8(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, void *q_row, void *s_row,
+                    void *q_col, void *s_col, int row_2d_block, int col_2d_block, int q_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(x_dtype == PTB_BF16 || x_dtype == PTB_F16, PTB_ERR_ARG, "MXFP8 quantise takes bf16 or fp16 input, got dtype %d", x_dtype);
+    PTB_REQUIRE(is_fp8(q_dtype), PTB_ERR_ARG, "MXFP8 quantise output must be e4m3 or e5m2, got dtype %d", q_dtype);
+    PTB_REQUIRE(G >= 0 && M >= 0 && N >= 0, PTB_ERR_ARG, "negative extent");
+    PTB_REQUIRE(N % kMxBlock == 0, PTB_ERR_ARG, "N (%lld) must be divisible by 32", (long long) N);
+    PTB_REQUIRE((q_row == nullptr) == (s_row == nullptr) && (q_col == nullptr) == (s_col == nullptr), PTB_ERR_ARG,
+                "each direction needs both its data and its scale output");
+    PTB_REQUIRE(q_row != nullptr || q_col != nullptr, PTB_ERR_ARG, "no output requested");
+    if (G == 0 || M == 0 || N == 0) return 0;
+    PTB_REQUIRE(aligned16(x) && (q_row == nullptr || aligned16(q_row)) && (q_col == nullptr || aligned16(q_col)), PTB_ERR_ARG,
+                "MXFP8 quantise needs 16-byte aligned input and FP8 outputs");
+    MxQuantArgs a;
+    a.x = x; a.q_row = (uint8_t *) q_row; a.s_row = (uint8_t *) s_row; a.q_col = (uint8_t *) q_col; a.s_col = (uint8_t *) s_col;
+    a.M = M; a.N = N; a.M_pad = cdiv<int64_t>(M, kMxPad) * kMxPad; a.N_pad = cdiv<int64_t>(N, kMxPad) * kMxPad;
+    a.row_2d = row_2d_block; a.col_2d = col_2d_block;
+    PTB_REQUIRE(a.M_pad / 128 <= 65535 && G <= 65535, PTB_ERR_ARG, "MXFP8 quantise: more than 65535 row tiles or groups");
+    dim3 grid((unsigned) (a.N_pad / 128), (unsigned) (a.M_pad / 128), (unsigned) G);
+    cudaStream_t st = (cudaStream_t) stream;
+    if (x_dtype == PTB_BF16) {
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__nv_bfloat16, FMT><<<grid, 256, 0, st>>>(a)));
+    } else {
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__half, FMT><<<grid, 256, 0, st>>>(a)));
+    }
+    PTB_LAUNCH_CHECK("mx_quant_kernel");
+    return 0;
+}
+
+int ptb_dequant_mxfp8(const void *q, int q_dtype, int64_t R, int64_t C, const void *scales, int transpose_out, void *out,
+                      int out_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(is_fp8(q_dtype) && is_hp(out_dtype), PTB_ERR_ARG, "MXFP8 dequantise: unsupported dtypes %d -> %d", q_dtype, out_dtype);
+    PTB_REQUIRE(R >= 0 && C >= 0 && C % kMxBlock == 0, PTB_ERR_ARG, "MXFP8 dequantise: the inner extent (%lld) must be divisible by 32", (long long) C);
+    if (R == 0 || C == 0) return 0;
+    PTB_REQUIRE(cdiv<int64_t>(R, 32) <= 65535, PTB_ERR_ARG, "MXFP8 dequantise: more than 65535 row tiles");
+    dim3 grid((unsigned) cdiv<int64_t>(C, 32), (unsigned) cdiv<int64_t>(R, 32));
+    cudaStream_t st = (cudaStream_t) stream;
+    const uint8_t *qq = (const uint8_t *) q, *ss = (const uint8_t *) scales;
+#define PTB_MX_DQ(TO)                                                                                          \
+    if (transpose_out) { PTB_SWITCH_FP8(q_dtype, FMT, (mx_dequant_kernel<TO, FMT, true><<<grid, 256, 0, st>>>(qq, ss, R, C, (TO *) out))); } \
+    else { PTB_SWITCH_FP8(q_dtype, FMT, (mx_dequant_kernel<TO, FMT, false><<<grid, 256, 0, st>>>(qq, ss, R, C, (TO *) out))); }
+    if (out_dtype == PTB_BF16) { PTB_MX_DQ(__nv_bfloat16) }
+    else if (out_dtype == PTB_F16) { PTB_MX_DQ(__half) }
+    else { PTB_MX_DQ(float) }
+#undef PTB_MX_DQ
+    PTB_LAUNCH_CHECK("mx_dequant_kernel");
+    return 0;
+}
+
+#pragma GCC visibility pop
+}

@@ -3,7 +3,8 @@
 Mirrors the names and semantics of primus_turbo/pytorch/core/low_precision.py:105-186 so that code
 written against the reference keeps working.  On B200 the FP8 types are always the OCP ones
 (e4m3fn / e5m2); the reference's FNUZ selection (low_precision.py:77-84) has no counterpart here.
-MX (1x32 E8M0) and FP4 recipes are declared for API compatibility but have no kernels.
+MXFP8 (1x32 blocks, E8M0 scales) has kernels for quantise / dequantise and the dense GEMM; the FP4
+recipes are declared for API compatibility but have no kernels.
 """
 
 from __future__ import annotations
@@ -22,6 +23,7 @@ float4_e2m1fn_x2 = getattr(torch, "float4_e2m1fn_x2", None)
 
 MXFP8_BLOCK_SIZE = 32
 MXFP4_BLOCK_SIZE = 32
+MXFP8_PADDING_ALIGN_SIZE = 128
 DEFAULT_BLOCK_SIZE = 128
 
 _FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e4m3fnuz, torch.float8_e5m2, torch.float8_e5m2fnuz)
@@ -46,7 +48,7 @@ def check_fp8_ocp_support() -> Tuple[bool, str]:
 
 
 def check_mxfp8_support() -> Tuple[bool, str]:
-    return False, "MXFP8 kernels are not part of this build."
+    return check_fp8_support()
 
 
 def check_mxfp4_support() -> Tuple[bool, str]:

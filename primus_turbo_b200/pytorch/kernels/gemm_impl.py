@@ -104,6 +104,30 @@ def gemm_fp8_impl(
     return out
 
 
+def gemm_mxfp8_impl(
+    a: torch.Tensor, a_scale_inv: torch.Tensor, b: torch.Tensor, b_scale_inv: torch.Tensor, out_dtype: torch.dtype,
+    num_sms: int = 0,
+) -> torch.Tensor:
+    """a [M, K_pad] . b [N, K_pad]^T with E8M0 scale bytes [rows, K_pad/32] applied by the block-scaled
+    tensor-core instruction.  The reference reaches this as gemm_fp8_impl(..., granularity=MX_BLOCKWISE)
+    with trans_a=False, trans_b=True (primus_turbo/pytorch/ops/gemm_fp8.py:582-640)."""
+    require_cuda(a, b, a_scale_inv, b_scale_inv)
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], "MX GEMM takes [M, K] and [N, K]"
+    a, b = _as_rows(a), _as_rows(b)
+    a_s, b_s = a_scale_inv.view(torch.uint8), b_scale_inv.view(torch.uint8)
+    assert a_s.stride(-1) == 1 and b_s.stride(-1) == 1
+    m, k = a.shape
+    n = b.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.call(
+            "ptb_gemm_mxfp8", ptr(a), dtype_code(a.dtype), a.stride(0), ptr(a_s), a_s.stride(0), ptr(b),
+            dtype_code(b.dtype), b.stride(0), ptr(b_s), b_s.stride(0), ptr(out), dtype_code(out_dtype), out.stride(0),
+            m, n, k, num_sms, stream_of(a),
+        )
+    return out
+
+
 def group_offs_from_lens(group_lens: torch.Tensor) -> torch.Tensor:
     """Exclusive prefix sum on the device (grouped_gemm_utils.py:28-34)."""
     assert group_lens.is_cuda, "group_lens must be on CUDA"

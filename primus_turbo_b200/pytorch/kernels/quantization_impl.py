@@ -272,3 +272,98 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
         _lib.call("ptb_gather_rows", ptr(xc), ptr(index.contiguous()), index.numel(), xc.shape[0], row_bytes, ptr(out),
                   stream_of(x))
     return out
+
+
+# ---- MXFP8 (1x32 blocks, E8M0 scale bytes) -------------------------------------------------------------
+MX_BLOCK = 32
+MX_PAD = 128
+E8M0 = torch.float8_e8m0fnu
+
+
+def quantize_mxfp8_impl(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    axis: int | None,
+    block_size: int,
+    with_trans: bool = False,
+    use_2d_block: bool = False,
+    use_2d_block_for_trans: bool | None = None,
+):
+    """x [M, N] or [G, M, N] (bf16 / fp16, contiguous).
+
+    with_trans=False: ``axis`` picks the direction -- 2-D: 1 = blocks along a row -> (q [M, N_pad],
+    scales [M, N_pad/32]); 0 = blocks along a column -> (q [N, M_pad], scales [N, M_pad/32], i.e. the
+    TRANSPOSED copy); 3-D: axis 2 / 1 likewise per group.  with_trans=True returns both directions
+    from one pass.  Scales have dtype float8_e8m0fnu.  Padded extents are multiples of 128.
+    (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:489-543,
+    csrc/pytorch/quantization/quantization.cpp:736-966 in the reference.)
+    """
+    require_cuda(x)
+    assert block_size == MX_BLOCK, f"The block size must be {MX_BLOCK} for MXFP8 quantization"
+    assert x.dtype in (torch.bfloat16, torch.float16), "Input must be BFloat16 or Half"
+    assert x.is_contiguous(), "Input must be contiguous"
+    assert x.dim() in (2, 3), f"The input tensor must be 2D or 3D but got {x.dim()}D."
+    batched = x.dim() == 3
+    G = x.shape[0] if batched else 1
+    M, N = x.shape[-2], x.shape[-1]
+    assert N % MX_BLOCK == 0, f"N must be divisible by {MX_BLOCK}"
+    if with_trans:
+        assert axis is None, "The axis must be None when with_trans is True."
+        want_row = want_col = True
+        col_2d = use_2d_block if use_2d_block_for_trans is None else use_2d_block_for_trans
+        row_2d = use_2d_block
+    else:
+        lo = 1 if batched else 0
+        assert axis in (lo, lo + 1), f"The axis must be {lo} or {lo + 1} when with_trans is False."
+        want_row, want_col = axis == lo + 1, axis == lo
+        row_2d = col_2d = use_2d_block
+    M_pad, N_pad = ceil_div(M, MX_PAD) * MX_PAD, ceil_div(N, MX_PAD) * MX_PAD
+    lead = (G,) if batched else ()
+    dev = x.device
+    q_row = s_row = q_col = s_col = None
+    if want_row:
+        q_row = torch.empty(lead + (M, N_pad), dtype=out_dtype, device=dev)
+        s_row = torch.empty(lead + (M, N_pad // MX_BLOCK), dtype=torch.uint8, device=dev)
+    if want_col:
+        q_col = torch.empty(lead + (N, M_pad), dtype=out_dtype, device=dev)
+        s_col = torch.empty(lead + (N, M_pad // MX_BLOCK), dtype=torch.uint8, device=dev)
+    if G * M * N > 0:
+        with torch.cuda.device(dev):
+            _lib.call(
+                "ptb_quant_mxfp8", ptr(x), dtype_code(x.dtype), G, M, N, ptr(q_row), ptr(s_row), ptr(q_col), ptr(s_col),
+                int(row_2d), int(col_2d), dtype_code(out_dtype), stream_of(x),
+            )
+    outs = []
+    if want_row:
+        outs += [q_row, s_row.view(E8M0)]
+    if want_col:
+        outs += [q_col, s_col.view(E8M0)]
+    return tuple(outs)
+
+
+def dequantize_mxfp8_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int, block_size: int, scale_inv: torch.Tensor):
+    """2-D: axis 1 -> [M, N_pad]; axis 0 (x is the transposed copy [N, M_pad]) -> [M_pad, N].  3-D: axis 2 ->
+    [G, M, N_pad]; axis 1 -> [G, M_pad, N].  (csrc/pytorch/quantization/quantization.cpp:283-358 in the reference.)"""
+    require_cuda(x, scale_inv)
+    assert block_size == MX_BLOCK, f"The block size must be {MX_BLOCK} for MXFP8 quantization"
+    assert x.is_contiguous() and scale_inv.is_contiguous()
+    assert x.dim() in (2, 3) and scale_inv.dim() == x.dim(), "scale_inv rank must match input"
+    assert scale_inv.dtype in (E8M0, torch.uint8), "scale_inv must be Float8_e8m0fnu / uint8 tensor"
+    lo = 1 if x.dim() == 3 else 0
+    assert axis in (lo, lo + 1)
+    rowwise = axis == lo + 1
+    R, C = x.shape[-2], x.shape[-1]
+    assert C % MX_BLOCK == 0, "The last dimension must be divisible by block_size"
+    G = x.shape[0] if x.dim() == 3 else 1
+    lead = (G,) if x.dim() == 3 else ()
+    out = torch.empty(lead + ((R, C) if rowwise else (C, R)), dtype=out_dtype, device=x.device)
+    s8 = scale_inv.view(torch.uint8)
+    with torch.cuda.device(x.device):
+        for g in range(G):
+            xg, sg, og = (x[g], s8[g], out[g]) if x.dim() == 3 else (x, s8, out)
+            if R * C > 0:
+                _lib.call(
+                    "ptb_dequant_mxfp8", ptr(xg), dtype_code(x.dtype), R, C, ptr(sg), 0 if rowwise else 1, ptr(og),
+                    dtype_code(out_dtype), stream_of(x),
+                )
+    return out

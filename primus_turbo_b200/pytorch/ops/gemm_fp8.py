@@ -9,6 +9,9 @@ defines the numbers a caller sees:
     along the other axis; grad_out is quantised twice from the original.
   * BLOCKWISE (:382-506): a -> 1x128 row copy + 128x1 column copy in one pass, b -> 128x128 tiles
     reused in backward, grad_out -> row + column copies.
+  * MX_BLOCKWISE (:509-647): every operand is quantised in both directions in one pass (1x32 blocks for
+    a and grad_out, 32x32 for b), the column copies are stored transposed, so forward, dgrad and wgrad
+    are all "NT" products of K-major operands whose E8M0 scales the tensor cores apply themselves.
 """
 
 from __future__ import annotations
@@ -31,6 +34,7 @@ from primus_turbo_b200.pytorch.core.quantized_tensor import (
     check_quantized_tensor,
 )
 from primus_turbo_b200.pytorch.kernels.custom_ops import gemm_fp8_impl
+from primus_turbo_b200.pytorch.kernels.gemm_impl import gemm_mxfp8_impl
 from primus_turbo_b200.pytorch.ops.quantization import quantize_fp8, quantize_fp8_with_trans
 
 __all__ = ["gemm_fp8"]
@@ -177,6 +181,39 @@ class FP8GemmBlockFunction(torch.autograd.Function):
         return grad_a, grad_b, None, None, None, None, None, None
 
 
+class FP8GemmMXFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, a_t, b_t, trans_a, trans_b, out_dtype, config):
+        assert trans_a == False and trans_b == True, "trans_a has to be False and trans_b has to be True"
+        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
+            raise NotImplementedError("MX_BLOCKWISE gemm_fp8 takes high-precision tensors in this build")
+        dt = _get_fp8_dtype(config.format, True)
+        a_row, a_row_s, a_col, a_col_s = quantize_fp8_with_trans(
+            a.contiguous(), dt, config.granularity, block_size=config.block_size, scaling_recipe=ScalingRecipe()
+        )
+        recipe = ScalingRecipe(use_2d_block=True)
+        b_row, b_row_s, b_col, b_col_s = quantize_fp8_with_trans(
+            b.contiguous(), dt, config.granularity, block_size=config.block_size, scaling_recipe=recipe,
+            scaling_recipe_for_trans=recipe,
+        )
+        out = gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, out_dtype)  # [M, K_pad] x [N, K_pad]^T
+        ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s)
+        ctx.out_dtype, ctx.config = out_dtype, config
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        a_col, a_col_s, b_col, b_col_s = ctx.saved_tensors
+        cfg = ctx.config
+        grad_out = grad_out.reshape(grad_out.shape[0], -1).contiguous()
+        g_row, g_row_s, g_col, g_col_s = quantize_fp8_with_trans(
+            grad_out, _get_fp8_dtype(cfg.format, False), cfg.granularity, block_size=cfg.block_size
+        )
+        grad_a = gemm_mxfp8_impl(g_row, g_row_s, b_col, b_col_s, ctx.out_dtype)  # [M, N_pad] x [K, N_pad]^T
+        grad_b = gemm_mxfp8_impl(g_col, g_col_s, a_col, a_col_s, ctx.out_dtype)  # [N, M_pad] x [K, M_pad]^T
+        return grad_a, grad_b, None, None, None, None, None, None
+
+
 @torch._dynamo.disable(recursive=True, reason="builds QuantizedTensor wrappers inside autograd.Function.forward")
 def gemm_fp8(
     a: Union[torch.Tensor, QuantizedTensor, QuantizedTensorPair],
@@ -206,4 +243,6 @@ def gemm_fp8(
         return FP8GemmRowFunction.apply(*args)
     if config.granularity == ScalingGranularity.BLOCKWISE:
         return FP8GemmBlockFunction.apply(*args)
+    if config.granularity == ScalingGranularity.MX_BLOCKWISE:
+        return FP8GemmMXFunction.apply(*args)
     raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

@@ -7,7 +7,9 @@ from typing import Optional, Tuple
 import torch
 
 from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
+from primus_turbo_b200.pytorch.core.low_precision import MXFP8_BLOCK_SIZE
 from primus_turbo_b200.pytorch.kernels import custom_ops as _ops
+from primus_turbo_b200.pytorch.kernels.quantization_impl import dequantize_mxfp8_impl, quantize_mxfp8_impl
 
 __all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8"]
 
@@ -40,7 +42,21 @@ def quantize_fp8(
             return _ops.quant_fp8_blockwise_for_weight(x, out_dtype, block_size)
         assert axis is not None, "axis must be specified for 1D BLOCKWISE quantization"
         return _ops.quant_fp8_blockwise(x, out_dtype, axis, block_size)
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        # x 2-D (axis 0: along columns, transposed copy; axis 1: along rows) or 3-D (axis 1 / 2); block 32
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        _reject_shuffle(scaling_recipe)
+        return quantize_mxfp8_impl(
+            x, out_dtype, axis, block_size, False, bool(scaling_recipe is not None and scaling_recipe.use_2d_block)
+        )
     raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def _reject_shuffle(recipe: Optional[ScalingRecipe]) -> None:
+    """The reference's pre-shuffled scale / data layouts feed its own GEMM back ends; this build's GEMM
+    reads the plain layouts, so the options are refused instead of silently ignored."""
+    if recipe is not None and (getattr(recipe, "shuffle_scale", False) or getattr(recipe, "shuffle_out", False)):
+        raise NotImplementedError("shuffled MXFP8 layouts are not part of this build")
 
 
 def quantize_fp8_with_trans(
@@ -56,6 +72,16 @@ def quantize_fp8_with_trans(
     if granularity == ScalingGranularity.BLOCKWISE:
         assert block_size is not None, "block_size must be specified for BLOCKWISE quantization"
         return _ops.quant_fp8_blockwise_dual(x, out_dtype, block_size)
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        # -> (row copy [.., M, N_pad], scales [.., M, N_pad/32], transposed column copy [.., N, M_pad], scales [.., N, M_pad/32])
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        _reject_shuffle(scaling_recipe)
+        _reject_shuffle(scaling_recipe_for_trans)
+        return quantize_mxfp8_impl(
+            x, out_dtype, None, block_size, True,
+            bool(scaling_recipe is not None and scaling_recipe.use_2d_block),
+            bool(scaling_recipe_for_trans is not None and scaling_recipe_for_trans.use_2d_block),
+        )
     raise NotImplementedError(f"Unknown granularity {granularity}")
 
 
@@ -81,4 +107,7 @@ def dequantize_fp8(
             return _ops.dequantize_fp8(x, scale_inv, out_dtype, 4, 0, block_size)
         assert axis is not None, "axis must be specified for 1D BLOCKWISE de-quantization"
         return _ops.dequantize_fp8(x, scale_inv, out_dtype, 3, axis, block_size)
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        return dequantize_mxfp8_impl(x, out_dtype, axis, block_size, scale_inv)
     raise NotImplementedError(f"Unknown granularity {granularity}")
