@@ -477,7 +477,10 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
     if (warp < 4) {
         // register split between the helper warpgroup and the two promotion warpgroups: the 1-D x 1-D
         // promotion needs every register it can get, the other modes leave more to the MMA issuer
+        // (in MX mode the scale loader keeps four blocks of scale words in registers and the epilogue holds no
+        // promotion state, so the split moves the other way)
         if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        else if constexpr (SCALE == kScaleMX) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
         else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
             // ================= TMA producer =================
@@ -630,15 +633,18 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
             }
             if constexpr (SCALE == kScaleMX) {
-                // Gathers each contraction block's scale bytes -- one aligned 32-bit word (four 32-wide
-                // slices) per operand row -- and lays them out as tcgen05.cp wants them: row r of a 128-row
-                // atom at byte 16 * (r % 32) + 4 * (r / 32), so a lane's four rows (lane, lane + 32, ...)
-                // are one 16-byte store.  The words of the next block are fetched before this block's are
-                // stored, so a global round trip is off the critical path inside a tile.
+                // Gathers the scale bytes of four contraction blocks at a time -- one aligned 16-byte load per
+                // operand row (a block's four 32-wide slices are one 32-bit word) -- and lays each block out
+                // as tcgen05.cp wants it: row r of a 128-row atom at byte 16 * (r % 32) + 4 * (r / 32), so a
+                // lane's four rows (lane, lane + 32, ...) are one 16-byte store.  The four-slot ring lets the
+                // loader run far enough ahead of the MMA issuer to hide the global round trip.
                 Schedule sched(args, ctl);
                 Tile t;
                 uint32_t it = 0;
                 bool ok     = true;
+                // rows of 16 scale bytes can be read with one vector load when the pitch and base allow it
+                const bool vec = (args.a_sf_ld % 16 == 0) && (args.b_sf_ld % 16 == 0) &&
+                                 ((reinterpret_cast<uintptr_t>(args.a_sf) | reinterpret_cast<uintptr_t>(args.b_sf)) & 15u) == 0;
                 while (ok && sched.get(t)) {
                     int row[12]; // operand rows whose scale words this lane moves (clamped: rows past the end are never stored)
 #pragma unroll
@@ -647,28 +653,35 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                         row[4 + i] = min(t.n0 + lane + 32 * i, args.N - 1);
                         row[8 + i] = min(t.n0 + 128 + lane + 32 * i, args.N - 1);
                     }
-                    auto fetch = [&](int i, int kb) {
-                        const uint8_t *base = i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld : args.b_sf + (int64_t) row[i] * args.b_sf_ld;
-                        return __ldg(reinterpret_cast<const uint32_t *>(base + 4 * kb));
-                    };
-                    uint32_t cur[12], nxt[12];
-#pragma unroll
-                    for (int i = 0; i < 12; ++i) cur[i] = t.num_kb > 0 ? fetch(i, 0) : 0u;
+                    uint4 w[12];
                     for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-                        if (kb + 1 < t.num_kb) {
+                        if ((kb & 3) == 0) {
 #pragma unroll
-                            for (int i = 0; i < 12; ++i) nxt[i] = fetch(i, kb + 1);
+                            for (int i = 0; i < 12; ++i) {
+                                const uint8_t *src = (i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld
+                                                            : args.b_sf + (int64_t) row[i] * args.b_sf_ld) + 4 * kb;
+                                if (vec && kb + 4 <= t.num_kb) {
+                                    w[i] = __ldg(reinterpret_cast<const uint4 *>(src));
+                                } else {
+                                    const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
+                                    w[i].x = __ldg(s32);
+                                    w[i].y = kb + 1 < t.num_kb ? __ldg(s32 + 1) : 0u;
+                                    w[i].z = kb + 2 < t.num_kb ? __ldg(s32 + 2) : 0u;
+                                    w[i].w = kb + 3 < t.num_kb ? __ldg(s32 + 3) : 0u;
+                                }
+                            }
                         }
                         const int slot = it % kScaleSlots;
                         if (!mbar_wait(smem_u32(&ctl->sc_empty[slot]), ((it / kScaleSlots) & 1) ^ 1)) { ok = false; break; }
                         const uint32_t dst = smem_u32(&ctl->scale_ring[slot * kSlotFloats]) + lane * 16;
-                        st_shared_v4(dst, make_uint4(cur[0], cur[1], cur[2], cur[3]));
-                        st_shared_v4(dst + 512, make_uint4(cur[4], cur[5], cur[6], cur[7]));
-                        st_shared_v4(dst + 1024, make_uint4(cur[8], cur[9], cur[10], cur[11]));
+                        const int q = kb & 3;
+#define PTB_SFW(i) (q == 0 ? w[i].x : q == 1 ? w[i].y : q == 2 ? w[i].z : w[i].w)
+                        st_shared_v4(dst, make_uint4(PTB_SFW(0), PTB_SFW(1), PTB_SFW(2), PTB_SFW(3)));
+                        st_shared_v4(dst + 512, make_uint4(PTB_SFW(4), PTB_SFW(5), PTB_SFW(6), PTB_SFW(7)));
+                        st_shared_v4(dst + 1024, make_uint4(PTB_SFW(8), PTB_SFW(9), PTB_SFW(10), PTB_SFW(11)));
+#undef PTB_SFW
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // tcgen05.cp reads through the async proxy
                         mbar_arrive(smem_u32(&ctl->sc_full[slot]));
-#pragma unroll
-                        for (int i = 0; i < 12; ++i) cur[i] = nxt[i];
                     }
                 }
                 if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
@@ -676,6 +689,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         }
     } else {
         if constexpr (SCALE == kScaleBlock1D) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        else if constexpr (SCALE == kScaleMX) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ================= promotion + epilogue warpgroups =================
         const int wg   = (warp - 4) >> 2;         // column slice of the tile this warp owns
@@ -997,10 +1011,15 @@ template <int SCALE> int launch_scale(const GemmArgs &args, int out_dtype, int g
     }
 }
 
+#ifndef PTB_MX_DEEP
+#define PTB_MX_DEEP 0
+#endif
+
 int launch_gemm(GemmArgs &args, int scale_mode, int out_dtype, int num_sms, cudaStream_t st) {
     // Tensorwise / rowwise scales keep the whole K loop in TMEM, so the epilogue is rare: spend the
     // staging buffer on a fourth pipeline stage instead (measured +8 % on 8192^3).
-    args.deep = ((scale_mode == kScaleTensor || scale_mode == kScaleRow) && args.kind == kKindDense) ? 1 : 0;
+    args.deep = ((scale_mode == kScaleTensor || scale_mode == kScaleRow || (scale_mode == kScaleMX && PTB_MX_DEEP)) &&
+                 args.kind == kKindDense) ? 1 : 0;
     int dev = 0, sms = 0;
     PTB_CUDA(cudaGetDevice(&dev));
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
