@@ -401,6 +401,9 @@ def _finish_line(args, line, kernel_ms, roofs, clocks, launches, status):
     print(json.dumps(line), flush=True)
 
 
+HOST_ENQUEUE_MS = [None]  # set by _timed: when it nears ms_per_step the host, not the GPU, paces the step
+
+
 def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None):
     """(ms per step, per-entry-point kernel times, clock summary, launches)"""
     from primus_turbo_b200 import _lib
@@ -414,8 +417,10 @@ def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None):
         if flush is None:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
+            h0 = time.perf_counter()
             for _ in range(steps):
                 step(*inputs)
+            HOST_ENQUEUE_MS[0] = (time.perf_counter() - h0) * 1e3 / steps  # host time to enqueue one step
             ev1.record()
             barrier()
             ms = ev0.elapsed_time(ev1) / steps
@@ -629,7 +634,8 @@ def run_grouped(args):
         cap = int(max(2 * ROWS // world, ROWS // world + 4096))
         try:
             # checks, on the host and on every rank alike, that all GPUs of the job can address each other
-            exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas)
+            exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas,
+                                    ordering=args.ep_ordering)
         except RuntimeError as exc:
             print(f"[bench] rank {rank}: {exc}; using NCCL all-to-alls", file=sys.stderr)
             exchange, args.exchange = None, "nccl"
@@ -683,6 +689,7 @@ def run_grouped(args):
     plan_ms.clear()
     ms, kernel_ms, clocks, launches = _timed(step, (a, gy), args.steps, args.warmup, barrier, local_rank)
     plan_host_ms = statistics.mean(plan_ms[-args.steps:]) if plan_ms else 0.0
+    host_enqueue_ms = HOST_ENQUEUE_MS[0]
     status = _lib.gemm_status()
     copy_status = _lib.copy_segments_status() if state["exchange"] is not None else 0
 
@@ -748,20 +755,24 @@ def run_grouped(args):
             _roof("ptb_quant_fp8_segment_row_col", "quant_block_kernel<row + padded column copy> (activation and grad-out)", 0,
                   (b_seg(K) + b_seg(N)) / 2, kernel_ms.get("ptb_quant_fp8_segment_row_col", []), peaks, fp8_peak),
         ]
-        if "ptb_copy_segments" in kernel_ms:
+        copy_key = "ptb_copy_segments_signal" if "ptb_copy_segments_signal" in kernel_ms else "ptb_copy_segments"
+        if copy_key in kernel_ms:
             sent = rows_here * (K + N) * 2 * 2 / 4  # mean bytes per launch over the step's four exchanges
-            r = _roof("ptb_copy_segments", "copy_segments_kernel (dispatch / combine over peer memory)", 0, sent,
-                      kernel_ms["ptb_copy_segments"], peaks, fp8_peak)
+            r = _roof(copy_key, "copy_segments_kernel (dispatch / combine over peer memory)", 0, sent,
+                      kernel_ms[copy_key], peaks, fp8_peak)
             r.update({"bound": "nvlink", "peak": 770.0, "peak_source": "measured peer copy, GB/s per direction",
                       "achieved": sent * (world - 1) / world / (r["avg_launch_ms"] * 1e-3) / 1e9})
             r["frac"] = r["achieved"] / r["peak"]
             roofs.append(r)
+        other_ms = {k: sum(kernel_ms.pop(k)) / args.steps for k in list(kernel_ms) if k.startswith("ep_")}
         step_kernels = sum(sum(v) for v in kernel_ms.values()) / args.steps
-        copy_k = sum(kernel_ms.get("ptb_copy_segments", [])) / args.steps
+        copy_k = sum(kernel_ms.get(copy_key, [])) / args.steps
+        wait_k = sum(kernel_ms.get("ptb_wait_flags", [])) / args.steps
         wl = _workload_config(args.config)
         wl.update({"experts": E, "routed_rows": ROWS, "experts_per_gpu": e_loc, "parallelism": f"ep{world}",
                    "exchange": (args.exchange if world > 1 else None), "placement": (args.placement if world > 1 else None),
                    "ep_overlap": (bool(args.ep_overlap) if world > 1 else None),
+                   "ep_ordering": (args.ep_ordering if world > 1 and args.exchange == "peer" else None),
                    "load_imbalance_max_over_mean_rows": imbalance,
                    "load_imbalance_contiguous_placement": imbalance_contiguous,
                    "tile_padding_rows_over_rows": pad0 / max(rows0, 1),
@@ -783,11 +794,14 @@ def run_grouped(args):
         if world > 1:
             line["ep_parity"] = ep_parity
             line["phases_ms"] = {"plan_host": plan_host_ms, "exchange_copy_kernels": copy_k,
-                                 "local_kernels": step_kernels - copy_k, "step": ms,
+                                 "local_kernels": step_kernels - copy_k - wait_k, "step": ms,
+                                 "host_enqueue": host_enqueue_ms,
+                                 "ordering": other_ms.get("ep_order_all_reduce", wait_k),
+                                 "copies_out_of_regions": other_ms.get("ep_copy_out_of_region"),
                                  "not_in_kernels": ms - step_kernels,
                                  "note": "rank 0's kernels; plan_host is host time that overlaps the device queue; "
-                                         "not_in_kernels covers the ordering collectives (or all-to-alls), "
-                                         "torch's copies and waiting for the slowest rank"}
+                                         "ordering (flag waits or all-reduces) includes waiting for the slowest rank; "
+                                         "not_in_kernels covers collectives, torch's copies and launch gaps"}
             line["copy_segments_status"] = copy_status
         _finish_line(args, line, kernel_ms, roofs, clocks, launches, status)
     if world > 1:
@@ -822,6 +836,9 @@ def main():
                     help="N > 1: experts assigned to ranks by greedy balancing of the expected load, or expert e on "
                          "rank e // (E/N)")
     ap.add_argument("--copy-ctas", type=int, default=0, help="CTAs of the peer copy kernel (0: one per SM)")
+    ap.add_argument("--ep-ordering", choices=["flags", "collective"], default="flags",
+                    help="how ranks order themselves after a peer exchange: arrival flags written by the copy kernel "
+                         "and a one-warp wait kernel, or a one-element all-reduce")
     ap.add_argument("--ep-overlap", type=int, default=0,
                     help="N > 1, peer exchange: 1 = weight quantise beside the dispatch and wgrad beside the return of "
                          "grad_a on a second stream (give --copy-ctas the same small number as --ep-reserve-sms)")

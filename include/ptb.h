@@ -202,6 +202,21 @@ int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
                       const int64_t *segments, int64_t nseg, int64_t row_bytes, int num_ctas,
                       ptb_stream_t stream);
 
+/* ptb_copy_segments that also tells every destination when this rank's rows have landed: after the
+ * copies (every thread fences its stores at system scope, the last CTA to finish acts) the kernel stores
+ * `seq` with release semantics into flag_slots[r] for every r -- this rank's 32-bit slot in rank r's flag
+ * array (peer-mapped like the buffers).  done_counter: a zeroed 32-bit word in local memory that the
+ * kernel leaves zero.  Runs (and signals) even when nseg == 0.  Sequence numbers of one slot must grow.
+ * ptb_wait_flags launches one warp that waits until flags[0..n) (local memory) have all reached seq;
+ * after 20 s it gives up, sets ptb_copy_segments_status to 2 and lets the stream go on.  Together they
+ * replace the collective that otherwise orders the ranks after an exchange.  n <= 32.
+ * No counterpart in the reference (its DeepEP port keeps such flags inside its own buffers). */
+int ptb_copy_segments_signal(const void *src_base, void *const *dst_bases, int n_ranks,
+                             const int64_t *segments, int64_t nseg, int64_t row_bytes, int num_ctas,
+                             void *const *flag_slots, void *done_counter, uint32_t seq,
+                             ptb_stream_t stream);
+int ptb_wait_flags(const void *flags, int n, uint32_t seq, ptb_stream_t stream);
+
 /* Lets kernels launched on the current device address memory that lives on peer_device (a device index of
  * this process): cudaDeviceEnablePeerAccess, treating "already enabled" as success.  Memory of another
  * process opened through a CUDA IPC handle is mapped for the device that was current when it was
@@ -209,8 +224,8 @@ int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
  * the two devices have no peer path.  No counterpart in the reference. */
 int ptb_enable_peer_access(int peer_device);
 
-/* Reads (and optionally clears) the flag a copy sets when its segment table named a bad
- * destination.  Synchronises with the device.  No counterpart in the reference. */
+/* Reads (and optionally clears) the status word: 1 when a copy's segment table named a bad
+ * destination, 2 when a flag wait ran out of time.  Synchronises with the device.  No counterpart in the reference. */
 int ptb_copy_segments_status(int *status, int reset);
 
 /* out[i, :] = in[index[i], :] for n_out rows of row_bytes bytes (a multiple of 16); an index outside
@@ -288,6 +303,25 @@ int ptb_quant_mxfp8(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N,
                     void *q_col, void *s_col, int row_2d_block, int col_2d_block, int q_dtype,
                     ptb_stream_t stream);
 
+/* Grouped form of ptb_quant_mxfp8 for x[M][N] whose rows form G groups (group_offs: device int64
+ * [G+1]): every group is quantised on its own, its rows padded with zeros to `row_align` rows (1 or 32)
+ * in the row-direction output and to 128 rows in the column-direction output:
+ *   q_row[M_row][N_pad] + s_row[M_row][N_pad/32]      M_row >= M + G*(row_align-1): only rows that
+ *                                                     exist are written, at row_offs_padded[g] + i;
+ *   q_col[N][M_col] + s_col[N][M_col/32], transposed, M_col = ceil((M + G*128)/128)*128: group g's
+ *                                                     rows at columns col_offs_padded[g] + i; every
+ *                                                     other column is written as zero.
+ * A block whose maximum is zero takes scale byte 127 (1.0), as the reference's grouped kernel does.
+ * Also written: the padded lengths and offsets of both layouts (device int64 [G] / [G+1]).
+ * block_table: workspace of 16 bytes per 128-row block of the column layout (M_col/128 blocks),
+ * 16-byte aligned.  Replaces grouped_quantize_mxfp8_dual
+ * (csrc/pytorch/quantization/quantization.cpp:1075-1195; the reference's row layout is row_align = 32). */
+int ptb_quant_mxfp8_grouped(const void *x, int x_dtype, int64_t M, int64_t N, const int64_t *group_offs,
+                            int64_t G, int64_t row_align, void *q_row, void *s_row, void *q_col,
+                            void *s_col, int64_t *row_lens_padded, int64_t *row_offs_padded,
+                            int64_t *col_lens_padded, int64_t *col_offs_padded, void *block_table,
+                            int row_2d_block, int col_2d_block, int q_dtype, ptb_stream_t stream);
+
 /* out = cast(float(q[R][C]) * 2^(scale byte - 127)) (byte 0 multiplies by 0.0f as the reference does),
  * scales[R][C/32]; transpose_out != 0 writes out[C][R] (the column-direction data come back as
  * [M_pad][N]).  Replaces dequantize_mxfp8 (quantization.cpp:283-358, dequantization_mxfp8.cu:47-100). */
@@ -305,6 +339,24 @@ int ptb_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, in
                    const void *b, int b_dtype, int64_t ldb, const void *b_sf, int64_t b_sf_ld, void *c,
                    int c_dtype, int64_t ldc, int64_t M, int64_t N, int64_t K, int num_sms,
                    ptb_stream_t stream);
+
+/* Grouped forms of ptb_gemm_mxfp8.
+ *   ptb_grouped_gemm_mxfp8: out[offs[g]:offs[g+1], :] = a[offs[g]:offs[g+1], :] . b[g]^T with a [M_total, K]
+ *   (+ a_sf [M_total, a_sf_ld]), b [G, N, K] and b_sf [G, N, K/32] contiguous; rows >= offs[G] zeroed.
+ *   ptb_grouped_gemm_mxfp8_variable_k: out[g] = lhs[:, offs[g]:offs[g+1]] . rhs[:, offs[g]:offs[g+1]]^T with the
+ *   transposed column copies lhs [OUT_M, rows_padded], rhs [OUT_N, rows_padded] of the grouped quantiser
+ *   (offsets multiples of 128: its col_offs_padded); an empty group gives a zero matrix.
+ * At most 1024 groups.  Replace grouped_gemm_fp8_impl / grouped_gemm_fp8_variable_k_impl with granularity
+ * MX_BLOCKWISE (primus_turbo/pytorch/ops/grouped_gemm_fp8.py:571-795). */
+int ptb_grouped_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, int64_t a_sf_ld,
+                           const void *b, int b_dtype, const void *b_sf, void *out, int out_dtype,
+                           int64_t ldc, const int64_t *group_offs, int64_t G, int64_t M_total, int64_t N,
+                           int64_t K, int num_sms, ptb_stream_t stream);
+int ptb_grouped_gemm_mxfp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_lhs, const void *lhs_sf,
+                                      int64_t lhs_sf_ld, const void *rhs, int rhs_dtype, int64_t ld_rhs,
+                                      const void *rhs_sf, int64_t rhs_sf_ld, void *out, int out_dtype,
+                                      const int64_t *group_offs_padded, int64_t G, int64_t rows_padded,
+                                      int64_t OUT_M, int64_t OUT_N, int num_sms, ptb_stream_t stream);
 
 /* Grouped GEMM over row segments of a (forward and dgrad of the MoE experts):
  *   out[offs[g]:offs[g+1], :] = a[offs[g]:offs[g+1], :] . op(b[g]),   rows >= offs[G] zeroed.

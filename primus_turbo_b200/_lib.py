@@ -53,6 +53,8 @@ _PROTOS = {
                              _I, _P],
     "ptb_grouped_gemm_fp8_variable_k": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _I, _P],
     "ptb_copy_segments": [_P, _P, _I, _P, _L, _L, _I, _P],
+    "ptb_copy_segments_signal": [_P, _P, _I, _P, _L, _L, _I, _P, _P, ctypes.c_uint32, _P],
+    "ptb_wait_flags": [_P, _I, ctypes.c_uint32, _P],
     "ptb_copy_segments_status": [ctypes.POINTER(c_int), _I],
     "ptb_enable_peer_access": [_I],
     "ptb_gather_rows": [_P, _P, _L, _L, _L, _P, _P],
@@ -65,6 +67,9 @@ _PROTOS = {
     "ptb_unpermute_rows_bwd": [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P, _P],
     "ptb_quant_mxfp8": [_P, _I, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "ptb_dequant_mxfp8": [_P, _I, _L, _L, _P, _I, _P, _I, _P],
+    "ptb_quant_mxfp8_grouped": [_P, _I, _L, _L, _P, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ptb_grouped_gemm_mxfp8": [_P, _I, _L, _P, _L, _P, _I, _P, _P, _I, _L, _P, _L, _L, _L, _L, _I, _P],
+    "ptb_grouped_gemm_mxfp8_variable_k": [_P, _I, _L, _P, _L, _P, _I, _L, _P, _L, _P, _I, _P, _L, _L, _L, _L, _I, _P],
     "ptb_gemm_mxfp8": [_P, _I, _L, _P, _L, _P, _I, _L, _P, _L, _P, _I, _L, _L, _L, _L, _I, _P],
     "ptb_gemm_status": [ctypes.POINTER(c_int), _I],
     "ptb_gemm_wait_selftest": [_P],
@@ -106,12 +111,13 @@ def check(rc: int, what: str) -> None:
 
 # kernels enqueued by one successful call of each entry point (memset nodes not counted)
 KERNELS_PER_CALL = {"ptb_quant_fp8_tensorwise": 2, "ptb_quant_fp8_rowwise": 2, "ptb_quant_fp8_rowwise_noalloc": 2,
-                    "ptb_quant_fp8_segment_row_col": 2, "ptb_moe_row_id_map": 3, "ptb_swiglu_quant_fp8_segment_row_col": 2,
+                    "ptb_quant_fp8_segment_row_col": 2, "ptb_quant_mxfp8_grouped": 2, "ptb_moe_row_id_map": 3, "ptb_swiglu_quant_fp8_segment_row_col": 2,
                     "ptb_gemm_status": 0, "ptb_copy_segments_status": 0, "ptb_enable_peer_access": 0}
 # PTB_DEBUG_STATUS=1: after every GEMM call, wait for the device and raise if a bounded wait inside the
 # kernel ran out (status codes in include/ptb.h).  Off by default: the check synchronises.
 _DEBUG_STATUS = os.environ.get("PTB_DEBUG_STATUS", "0") not in ("", "0")
-_GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_gemm_mxfp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k")
+_GEMM_ENTRY_POINTS = ("ptb_gemm_fp8", "ptb_gemm_mxfp8", "ptb_grouped_gemm_fp8", "ptb_grouped_gemm_fp8_variable_k",
+                      "ptb_grouped_gemm_mxfp8", "ptb_grouped_gemm_mxfp8_variable_k")
 # PTB_NVTX=1: one NVTX range per C-ABI call, named after the entry point (timeline tools show them)
 _NVTX = os.environ.get("PTB_NVTX", "0") not in ("", "0")
 launch_count = 0  # running total of kernels this process enqueued through the C ABI
@@ -147,6 +153,28 @@ def call(name: str, *args) -> None:
         code = gemm_status(reset=True)
         if code != 0:
             raise PtbError(f"{name}: a device-side wait ran out (status {code}); the output is incomplete")
+
+
+class timed_region:
+    """Brackets other device work (a collective, a torch copy) with events under ``name`` while
+    ``record_kernel_times`` is active, so that a step's timeline can be accounted for; otherwise free."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        self.log = _event_log
+        if self.log is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.log is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.log.setdefault(self.name, []).append((self.e0, e1))
+        return False
 
 
 class record_kernel_times:

@@ -6,8 +6,11 @@
 // such segment starts in the destination's buffer.  One kernel copies all segments of a rank with plain
 // 16-byte loads from local memory and plain 16-byte stores to the destination -- peer memory mapped
 // into this process (NVLink / NVSwitch) or local memory for the rank's own share -- so rows land in
-// expert-major order, ready for the grouped GEMM, with no staging pass on either side.  The kernel
-// waits on nothing; the ranks order themselves with a collective afterwards.
+// expert-major order, ready for the grouped GEMM, with no staging pass on either side.  The copy kernel
+// waits on nothing.  Ordering between ranks: either a collective afterwards, or the copy's own signal --
+// the last CTA to finish stores the exchange's sequence number into a slot of every destination's flag
+// array (release, system scope, after every thread has fenced its data stores), and the destination runs
+// a one-warp kernel that waits, with a time limit, until all sources' slots carry that number.
 #include "ptb_common.cuh"
 
 namespace ptb {
@@ -25,9 +28,25 @@ struct CopyArgs {
     int nseg;
     int n_ranks;
     int64_t row_bytes;
+    // optional arrival signal (done == nullptr: none)
+    uint32_t *flag[kMaxPeers]; // per destination rank: this rank's slot in that rank's flag array
+    uint32_t *done;            // local counter of finished CTAs, zero between launches
+    uint32_t seq;
 };
 
-// set to 1 by a copy whose segment table names a rank outside [0, n_ranks) (that segment is skipped)
+constexpr uint64_t kFlagWaitLimitNs = 20000000000ull; // 20 s: ranks of one job are never this far apart
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// set to 1 by a copy whose segment table names a rank outside [0, n_ranks) (that segment is skipped),
+// to 2 by a flag wait that ran out of time
 __device__ int g_copy_error = 0;
 
 __global__ void __launch_bounds__(kCopyThreads) copy_segments_kernel(const CopyArgs a) {
@@ -90,6 +109,37 @@ __global__ void __launch_bounds__(kCopyThreads) copy_segments_kernel(const CopyA
         for (int i = 0; i < 4; ++i) {
             const int j = tid + i * kCopyThreads;
             if (j < nvec) dst[j] = v[i];
+        }
+    }
+    if (a.done != nullptr) {
+        __threadfence_system(); // this thread's stores, wherever they went, before the CTA counts itself
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            if (atomicAdd(a.done, 1u) == gridDim.x - 1) {
+                __threadfence_system();
+                for (int r = 0; r < a.n_ranks; ++r) st_release_sys(a.flag[r], a.seq);
+                *a.done = 0; // the next launch on this stream starts after this kernel has ended
+            }
+        }
+    }
+}
+
+// One warp: lane r waits until flags[r] has reached `seq` (sequence numbers only grow; the comparison
+// survives wrap-around).  On expiry it records the failure and returns -- the stream goes on with
+// whatever arrived, and the host finds the status word set.
+__global__ void __launch_bounds__(32) wait_flags_kernel(const uint32_t *flags, int n, uint32_t seq) {
+    const int r = threadIdx.x;
+    if (r >= n) return;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    while ((int32_t) (ld_acquire_sys(flags + r) - seq) < 0) {
+        __nanosleep(100);
+        uint64_t t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > kFlagWaitLimitNs) {
+            atomicExch(&g_copy_error, 2);
+            break;
         }
     }
 }
@@ -265,15 +315,40 @@ using namespace ptb;
 extern "C" {
 #pragma GCC visibility push(default)
 
+static int copy_segments_impl(const void *src_base, void *const *dst_bases, int n_ranks, const int64_t *segments,
+                              int64_t nseg, int64_t row_bytes, int num_ctas, void *const *flag_slots, void *done_counter,
+                              uint32_t seq, ptb_stream_t stream);
+
 int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks, const int64_t *segments, int64_t nseg,
                       int64_t row_bytes, int num_ctas, ptb_stream_t stream) {
+    return copy_segments_impl(src_base, dst_bases, n_ranks, segments, nseg, row_bytes, num_ctas, nullptr, nullptr, 0, stream);
+}
+
+int ptb_copy_segments_signal(const void *src_base, void *const *dst_bases, int n_ranks, const int64_t *segments,
+                             int64_t nseg, int64_t row_bytes, int num_ctas, void *const *flag_slots, void *done_counter,
+                             uint32_t seq, ptb_stream_t stream) {
+    PTB_REQUIRE(flag_slots && done_counter, PTB_ERR_ARG, "copy_segments_signal: null flag slots or counter");
+    return copy_segments_impl(src_base, dst_bases, n_ranks, segments, nseg, row_bytes, num_ctas, flag_slots, done_counter, seq,
+                              stream);
+}
+
+int ptb_wait_flags(const void *flags, int n, uint32_t seq, ptb_stream_t stream) {
+    PTB_REQUIRE(flags && n >= 1 && n <= 32, PTB_ERR_ARG, "wait_flags: 1 to 32 flags");
+    wait_flags_kernel<<<1, 32, 0, (cudaStream_t) stream>>>((const uint32_t *) flags, n, seq);
+    PTB_LAUNCH_CHECK("wait_flags_kernel");
+    return 0;
+}
+
+static int copy_segments_impl(const void *src_base, void *const *dst_bases, int n_ranks, const int64_t *segments,
+                              int64_t nseg, int64_t row_bytes, int num_ctas, void *const *flag_slots, void *done_counter,
+                              uint32_t seq, ptb_stream_t stream) {
     PTB_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers, PTB_ERR_TOO_LARGE, "copy_segments: 1 to %d ranks, got %d", kMaxPeers,
                 n_ranks);
     PTB_REQUIRE(nseg >= 0 && nseg <= kMaxSegments, PTB_ERR_TOO_LARGE, "copy_segments: at most %d segments", kMaxSegments);
     PTB_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, PTB_ERR_ALIGN, "copy_segments: row size %lld is not a multiple of 16 bytes",
                 (long long) row_bytes);
-    if (nseg == 0) return 0;
-    PTB_REQUIRE(src_base && dst_bases && segments, PTB_ERR_ARG, "copy_segments: null pointer");
+    if (nseg == 0 && flag_slots == nullptr) return 0;
+    PTB_REQUIRE(dst_bases && (nseg == 0 || (src_base && segments)), PTB_ERR_ARG, "copy_segments: null pointer");
     PTB_REQUIRE(aligned16(src_base), PTB_ERR_ALIGN, "copy_segments: source is not 16-byte aligned");
     CopyArgs a{};
     a.src = (const uint8_t *) src_base;
@@ -283,6 +358,15 @@ int ptb_copy_segments(const void *src_base, void *const *dst_bases, int n_ranks,
         a.dst[r] = (uint8_t *) dst_bases[r];
     }
     a.segs = segments; a.nseg = (int) nseg; a.n_ranks = n_ranks; a.row_bytes = row_bytes;
+    if (flag_slots != nullptr) {
+        for (int r = 0; r < n_ranks; ++r) {
+            PTB_REQUIRE(flag_slots[r] && (reinterpret_cast<uintptr_t>(flag_slots[r]) & 3u) == 0, PTB_ERR_ALIGN,
+                        "copy_segments_signal: flag slot of rank %d is null or misaligned", r);
+            a.flag[r] = (uint32_t *) flag_slots[r];
+        }
+        a.done = (uint32_t *) done_counter;
+        a.seq  = seq;
+    }
     int dev = 0, sms = 0;
     PTB_CUDA(cudaGetDevice(&dev));
     PTB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

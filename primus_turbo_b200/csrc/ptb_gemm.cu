@@ -653,14 +653,19 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                         row[4 + i] = min(t.n0 + lane + 32 * i, args.N - 1);
                         row[8 + i] = min(t.n0 + 128 + lane + 32 * i, args.N - 1);
                     }
+                    // per-expert weights: B's scale rows follow the groups; variable-K groups: the scale bytes of
+                    // contraction rows [k_row0, ...) start k_row0 / 32 bytes into every operand row
+                    const int64_t b_row0 = (args.kind == kKindGroupedRows) ? (int64_t) t.g * args.N : 0;
+                    const int k_byte0    = t.k_row0 / 32;
+                    const bool vec_t     = vec && ((k_byte0 & 15) == 0);
                     uint4 w[12];
                     for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
                         if ((kb & 3) == 0) {
 #pragma unroll
                             for (int i = 0; i < 12; ++i) {
                                 const uint8_t *src = (i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld
-                                                            : args.b_sf + (int64_t) row[i] * args.b_sf_ld) + 4 * kb;
-                                if (vec && kb + 4 <= t.num_kb) {
+                                                            : args.b_sf + (b_row0 + row[i]) * args.b_sf_ld) + k_byte0 + 4 * kb;
+                                if (vec_t && kb + 4 <= t.num_kb) {
                                     w[i] = __ldg(reinterpret_cast<const uint4 *>(src));
                                 } else {
                                     const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
@@ -1142,6 +1147,79 @@ int ptb_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, in
     if (rc) return rc;
     g.a_sf = (const uint8_t *) a_sf; g.a_sf_ld = a_sf_ld; g.b_sf = (const uint8_t *) b_sf; g.b_sf_ld = b_sf_ld;
     return launch_gemm(g, kScaleMX, c_dtype, num_sms, (cudaStream_t) stream);
+}
+
+int ptb_grouped_gemm_mxfp8(const void *a, int a_dtype, int64_t lda, const void *a_sf, int64_t a_sf_ld, const void *b,
+                           int b_dtype, const void *b_sf, void *out, int out_dtype, int64_t ldc, const int64_t *group_offs,
+                           int64_t G, int64_t M_total, int64_t N, int64_t K, int num_sms, ptb_stream_t stream) {
+    PTB_REQUIRE(G >= 0 && M_total >= 0 && N >= 0 && K > 0, PTB_ERR_ARG, "grouped_gemm_mxfp8: bad shape");
+    if (M_total == 0 || N == 0) return 0;
+    PTB_REQUIRE(G > 0 && G <= kMaxGroups, PTB_ERR_TOO_LARGE, "grouped_gemm_mxfp8: 1 to %d groups", kMaxGroups);
+    PTB_REQUIRE(a && b && out && group_offs && a_sf && b_sf, PTB_ERR_ARG, "grouped_gemm_mxfp8: null pointer");
+    PTB_REQUIRE(is_fp8(a_dtype) && is_fp8(b_dtype), PTB_ERR_ARG, "grouped_gemm_mxfp8: operands must be FP8");
+    PTB_REQUIRE(M_total < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && G * N < (1ll << 31), PTB_ERR_TOO_LARGE,
+                "grouped_gemm_mxfp8: dimension too large");
+    PTB_REQUIRE(K % BK == 0, PTB_ERR_ARG, "grouped_gemm_mxfp8: the (padded) contraction extent %lld must be a multiple of 128",
+                (long long) K);
+    PTB_REQUIRE(a_sf_ld >= K / 32 && a_sf_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(a_sf) & 3u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(b_sf) & 3u) == 0,
+                PTB_ERR_ALIGN, "grouped_gemm_mxfp8: scale rows must hold K/32 bytes, be 4-byte aligned and a multiple of 4 apart");
+    GemmArgs g{};
+    const int BN = kTileN;
+    g.bn         = BN;
+    int rc = make_map(&g.tm_a, a, (uint64_t) K, (uint64_t) M_total, 1, (uint64_t) lda, (uint64_t) lda * M_total, BM);
+    if (rc) return rc;
+    rc = make_map(&g.tm_b, b, (uint64_t) K, (uint64_t) N, (uint64_t) G, (uint64_t) K, (uint64_t) K * N, BN);
+    if (rc) return rc;
+    g.kind = kKindGroupedRows; g.a_mn = 0; g.b_mn = 0;
+    g.idesc = make_idesc_mx(a_dtype, b_dtype, BN);
+    g.M = (int) M_total; g.N = (int) N; g.K = (int) K; g.G = (int) G;
+    g.tiles_n = (int) cdiv<int64_t>(N, BN);
+    g.group_offs = group_offs;
+    g.c = out; g.ldc = ldc; g.c_group_stride = 0;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, out, out_dtype, (uint64_t) N, (uint64_t) M_total, 1, (uint64_t) ldc, 0);
+    if (rc) return rc;
+    g.a_sf = (const uint8_t *) a_sf; g.a_sf_ld = a_sf_ld; g.b_sf = (const uint8_t *) b_sf; g.b_sf_ld = K / 32;
+    return launch_gemm(g, kScaleMX, out_dtype, num_sms, (cudaStream_t) stream);
+}
+
+int ptb_grouped_gemm_mxfp8_variable_k(const void *lhs, int lhs_dtype, int64_t ld_lhs, const void *lhs_sf, int64_t lhs_sf_ld,
+                                      const void *rhs, int rhs_dtype, int64_t ld_rhs, const void *rhs_sf, int64_t rhs_sf_ld,
+                                      void *out, int out_dtype, const int64_t *group_offs_padded, int64_t G, int64_t rows_padded,
+                                      int64_t OUT_M, int64_t OUT_N, int num_sms, ptb_stream_t stream) {
+    PTB_REQUIRE(G >= 0 && rows_padded >= 0 && OUT_M >= 0 && OUT_N >= 0, PTB_ERR_ARG, "grouped_gemm_mxfp8_variable_k: bad shape");
+    if (G == 0 || OUT_M == 0 || OUT_N == 0) return 0;
+    PTB_REQUIRE(lhs && rhs && out && group_offs_padded && lhs_sf && rhs_sf, PTB_ERR_ARG,
+                "grouped_gemm_mxfp8_variable_k: null pointer");
+    PTB_REQUIRE(is_fp8(lhs_dtype) && is_fp8(rhs_dtype), PTB_ERR_ARG, "grouped_gemm_mxfp8_variable_k: operands must be FP8");
+    PTB_REQUIRE(G <= kMaxGroups, PTB_ERR_TOO_LARGE, "grouped_gemm_mxfp8_variable_k: at most %d groups", kMaxGroups);
+    PTB_REQUIRE(rows_padded % BK == 0, PTB_ERR_ARG, "grouped_gemm_mxfp8_variable_k: padded rows must be a multiple of 128");
+    PTB_REQUIRE(rows_padded < (1ll << 31) && OUT_M < (1ll << 31) && OUT_N < (1ll << 31) &&
+                    G * cdiv<int64_t>(OUT_M, BM) * cdiv<int64_t>(OUT_N, 128) < (1ll << 31),
+                PTB_ERR_TOO_LARGE, "grouped_gemm_mxfp8_variable_k: problem too large");
+    PTB_REQUIRE(lhs_sf_ld >= rows_padded / 32 && rhs_sf_ld >= rows_padded / 32 && lhs_sf_ld % 4 == 0 && rhs_sf_ld % 4 == 0 &&
+                    (reinterpret_cast<uintptr_t>(lhs_sf) & 3u) == 0 && (reinterpret_cast<uintptr_t>(rhs_sf) & 3u) == 0,
+                PTB_ERR_ALIGN, "grouped_gemm_mxfp8_variable_k: scale rows must be 4-byte aligned and a multiple of 4 apart");
+    GemmArgs g{};
+    const int BN = kTileN;
+    g.bn         = BN;
+    const uint64_t r = rows_padded > 0 ? (uint64_t) rows_padded : 1;
+    // both operands are transposed copies: [OUT_M, rows] and [OUT_N, rows], contraction axis contiguous
+    int rc = make_map(&g.tm_a, lhs, r, (uint64_t) OUT_M, 1, (uint64_t) ld_lhs, (uint64_t) ld_lhs * OUT_M, BM);
+    if (rc) return rc;
+    rc = make_map(&g.tm_b, rhs, r, (uint64_t) OUT_N, 1, (uint64_t) ld_rhs, (uint64_t) ld_rhs * OUT_N, BN);
+    if (rc) return rc;
+    g.kind = kKindGroupedK; g.a_mn = 0; g.b_mn = 0;
+    g.idesc = make_idesc_mx(lhs_dtype, rhs_dtype, BN);
+    g.M = (int) OUT_M; g.N = (int) OUT_N; g.K = (int) rows_padded; g.G = (int) G;
+    g.tiles_n = (int) cdiv<int64_t>(OUT_N, BN);
+    g.group_offs = group_offs_padded;
+    g.c = out; g.ldc = OUT_N; g.c_group_stride = OUT_M * OUT_N;
+    rc = make_c_map(&g.tm_c, &g.use_tma_store, out, out_dtype, (uint64_t) OUT_N, (uint64_t) OUT_M, (uint64_t) G,
+                    (uint64_t) OUT_N, (uint64_t) (OUT_M * OUT_N));
+    if (rc) return rc;
+    g.a_sf = (const uint8_t *) lhs_sf; g.a_sf_ld = lhs_sf_ld; g.b_sf = (const uint8_t *) rhs_sf; g.b_sf_ld = rhs_sf_ld;
+    return launch_gemm(g, kScaleMX, out_dtype, num_sms, (cudaStream_t) stream);
 }
 
 int ptb_grouped_gemm_fp8(const void *a, int a_dtype, int64_t lda, const void *b, int b_dtype, int trans_b, void *out,

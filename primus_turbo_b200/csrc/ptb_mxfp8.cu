@@ -40,6 +40,10 @@ template <int FMT> __device__ __forceinline__ int mx_biased_exponent(float amax)
     e                   = min(e, 128);
     return e + 127;
 }
+template <int FMT, bool ZERO_IS_ONE> __device__ __forceinline__ int mx_byte(float amax) {
+    if (ZERO_IS_ONE && amax == 0.0f) return 127;
+    return mx_biased_exponent<FMT>(amax);
+}
 // The clamp limit fmax * (byte << 23 read as fp32) -- byte 0 gives 0.0f, byte 255 gives +inf, as in the
 // reference -- and the exact reciprocal 2^(127 - byte) (subnormal for bytes 254 and 255).
 template <int FMT> __device__ __forceinline__ void mx_limits(int biased, float &lim, float &inv) {
@@ -53,7 +57,53 @@ struct MxQuantArgs {
     uint8_t *q_row, *s_row, *q_col, *s_col;
     int64_t M, N, M_pad, N_pad;
     int row_2d, col_2d;
+    // grouped mode: per 128-row block of the padded column layout {first source row, end of the group's
+    // source rows, row of the row-direction output that the first source row goes to, group}
+    const int4 *table;
 };
+
+// Grouped layouts (csrc/pytorch/quantization/quantization.cpp:1100-1130 in the reference): every group's rows
+// padded to `row_align` rows in the row-direction output and to 128 rows in the column-direction output.
+// One CTA: padded lengths and offsets of both layouts and the block table of MxQuantArgs; blocks past the
+// last group get an empty entry (they are written as zeros).
+__global__ void __launch_bounds__(256) mx_group_layout_kernel(const int64_t *__restrict__ group_offs, int64_t G, int64_t row_align,
+                                                              int64_t *__restrict__ row_lens, int64_t *__restrict__ row_offs,
+                                                              int64_t *__restrict__ col_lens, int64_t *__restrict__ col_offs,
+                                                              int4 *__restrict__ table, int64_t nblocks) {
+    __shared__ int64_t s_row[256], s_col[256];
+    const int tid     = threadIdx.x;
+    const int64_t per = cdiv<int64_t>(G, 256);
+    const int64_t g0 = (int64_t) tid * per, g1 = imin(g0 + per, G);
+    int64_t lr = 0, lc = 0;
+    for (int64_t g = g0; g < g1; ++g) {
+        const int64_t len = group_offs[g + 1] - group_offs[g];
+        lr += cdiv<int64_t>(len, row_align) * row_align;
+        lc += cdiv<int64_t>(len, kMxPad) * kMxPad;
+    }
+    s_row[tid] = lr;
+    s_col[tid] = lc;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+        const int64_t ar = (tid >= off) ? s_row[tid - off] : 0, ac = (tid >= off) ? s_col[tid - off] : 0;
+        __syncthreads();
+        s_row[tid] += ar;
+        s_col[tid] += ac;
+        __syncthreads();
+    }
+    int64_t run_r = s_row[tid] - lr, run_c = s_col[tid] - lc;
+    for (int64_t g = g0; g < g1; ++g) {
+        const int64_t gs = group_offs[g], ge = group_offs[g + 1];
+        const int64_t pr = cdiv<int64_t>(ge - gs, row_align) * row_align, pc = cdiv<int64_t>(ge - gs, kMxPad) * kMxPad;
+        row_lens[g] = pr; row_offs[g] = run_r;
+        col_lens[g] = pc; col_offs[g] = run_c;
+        for (int64_t t = 0; t < pc / kMxPad; ++t)
+            table[run_c / kMxPad + t] = make_int4((int) (gs + t * kMxPad), (int) ge, (int) (run_r + t * kMxPad), (int) g);
+        run_r += pr;
+        run_c += pc;
+    }
+    if (tid == 255) { row_offs[G] = s_row[255]; col_offs[G] = s_col[255]; }
+    for (int64_t b = s_col[255] / kMxPad + tid; b < nblocks; b += 256) table[b] = make_int4(0, 0, 0, -1);
+}
 
 template <typename T> __device__ __forceinline__ void decode8(const uint4 &raw, float (&v)[8]) {
     const T *e = reinterpret_cast<const T *>(&raw);
@@ -69,20 +119,31 @@ template <int FMT> __device__ __forceinline__ uint32_t mx_cvt4(const float *v, f
 }
 
 // grid: (N_pad / 128, M_pad / 128, G); 256 threads; warp w: rows 32 * (w & 3), columns 64 * (w >> 2)
-template <typename T, int FMT> __global__ void __launch_bounds__(256, PTB_MXQ_MINB) mx_quant_kernel(const MxQuantArgs p) {
+// GROUPED: blockIdx.y walks the 128-row blocks of the padded column layout; the block table says which
+// source rows it holds and where they go in the row-direction output; a block maximum of zero takes scale
+// byte 127 (1.0) instead of 0, as the reference's grouped kernel does (quantization_mxfp8.cu:1425-1450).
+template <typename T, int FMT, bool GROUPED>
+__global__ void __launch_bounds__(256, PTB_MXQ_MINB) mx_quant_kernel(const MxQuantArgs p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rl = lane >> 3, cl = lane & 7;
-    const int64_t g    = blockIdx.z;
-    const int64_t row0 = (int64_t) blockIdx.y * 128 + 32 * (warp & 3);
+    const int64_t g    = GROUPED ? 0 : blockIdx.z;
+    const int64_t row0 = (int64_t) blockIdx.y * 128 + 32 * (warp & 3); // row of the (padded) column layout
     const int64_t col0 = (int64_t) blockIdx.x * 128 + 64 * (warp >> 2);
     const int64_t col  = col0 + cl * 8;
     const T *x         = reinterpret_cast<const T *>(p.x) + g * p.M * p.N;
+    int64_t src0 = row0, src_end = p.M, out0 = row0; // first source row of this warp, end of valid rows, its row-output row
+    if constexpr (GROUPED) {
+        const int4 e = p.table[blockIdx.y];
+        src0         = (int64_t) e.x + 32 * (warp & 3);
+        src_end      = e.y;
+        out0         = (int64_t) e.z + 32 * (warp & 3);
+    }
 
     uint4 raw[8];
 #pragma unroll
     for (int ps = 0; ps < 8; ++ps) {
-        const int64_t r = row0 + 4 * ps + rl;
-        raw[ps]         = (r < p.M && col < p.N) ? *reinterpret_cast<const uint4 *>(x + r * p.N + col) : make_uint4(0, 0, 0, 0);
+        const int64_t r = src0 + 4 * ps + rl;
+        raw[ps]         = (r < src_end && col < p.N) ? *reinterpret_cast<const uint4 *>(x + r * p.N + col) : make_uint4(0, 0, 0, 0);
     }
     float rmax[8], cmax[8];
 #pragma unroll
@@ -118,12 +179,12 @@ template <typename T, int FMT> __global__ void __launch_bounds__(256, PTB_MXQ_MI
     if (p.q_row != nullptr) {
         uint8_t *q       = p.q_row + g * p.M * p.N_pad;
         uint8_t *s       = p.s_row + g * p.M * (p.N_pad / kMxBlock);
-        const int tile_b = mx_biased_exponent<FMT>(tmax);
+        const int tile_b = mx_byte<FMT, GROUPED>(tmax);
 #pragma unroll
         for (int ps = 0; ps < 8; ++ps) {
-            const int64_t r = row0 + 4 * ps + rl;
-            if (r >= p.M) continue;
-            const int biased = p.row_2d ? tile_b : mx_biased_exponent<FMT>(rmax[ps]);
+            if (src0 + 4 * ps + rl >= src_end) continue; // only rows that exist are written
+            const int64_t r  = out0 + 4 * ps + rl;
+            const int biased = p.row_2d ? tile_b : mx_byte<FMT, GROUPED>(rmax[ps]);
             float lim, inv;
             mx_limits<FMT>(biased, lim, inv);
             float v[8];
@@ -137,7 +198,7 @@ template <typename T, int FMT> __global__ void __launch_bounds__(256, PTB_MXQ_MI
     if (p.q_col != nullptr) {
         uint8_t *q = p.q_col + g * p.N * p.M_pad;
         uint8_t *s = p.s_col + g * p.N * (p.M_pad / kMxBlock);
-        const int tile_b = mx_biased_exponent<FMT>(tmax);
+        const int tile_b = mx_byte<FMT, GROUPED>(tmax);
         // two passes of four columns each keep the live state small
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -145,7 +206,7 @@ template <typename T, int FMT> __global__ void __launch_bounds__(256, PTB_MXQ_MI
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int j      = 4 * h + i;
-                const int biased = p.col_2d ? tile_b : mx_biased_exponent<FMT>(cmax[j]);
+                const int biased = p.col_2d ? tile_b : mx_byte<FMT, GROUPED>(cmax[j]);
                 mx_limits<FMT>(biased, lim[i], inv[i]);
                 if (rl == 0 && col + j < p.N) s[(col + j) * (p.M_pad / kMxBlock) + row0 / kMxBlock] = (uint8_t) biased;
             }
@@ -235,10 +296,50 @@ int ptb_quant_mxfp8(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N,
     PTB_REQUIRE(a.M_pad / 128 <= 65535 && G <= 65535, PTB_ERR_ARG, "MXFP8 quantise: more than 65535 row tiles or groups");
     dim3 grid((unsigned) (a.N_pad / 128), (unsigned) (a.M_pad / 128), (unsigned) G);
     cudaStream_t st = (cudaStream_t) stream;
+    a.table = nullptr;
     if (x_dtype == PTB_BF16) {
-        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__nv_bfloat16, FMT><<<grid, 256, 0, st>>>(a)));
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__nv_bfloat16, FMT, false><<<grid, 256, 0, st>>>(a)));
     } else {
-        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__half, FMT><<<grid, 256, 0, st>>>(a)));
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__half, FMT, false><<<grid, 256, 0, st>>>(a)));
+    }
+    PTB_LAUNCH_CHECK("mx_quant_kernel");
+    return 0;
+}
+
+int ptb_quant_mxfp8_grouped(const void *x, int x_dtype, int64_t M, int64_t N, const int64_t *group_offs, int64_t G,
+                            int64_t row_align, void *q_row, void *s_row, void *q_col, void *s_col, int64_t *row_lens_padded,
+                            int64_t *row_offs_padded, int64_t *col_lens_padded, int64_t *col_offs_padded, void *block_table,
+                            int row_2d_block, int col_2d_block, int q_dtype, ptb_stream_t stream) {
+    PTB_REQUIRE(x_dtype == PTB_BF16 || x_dtype == PTB_F16, PTB_ERR_ARG, "MXFP8 quantise takes bf16 or fp16 input, got dtype %d", x_dtype);
+    PTB_REQUIRE(is_fp8(q_dtype), PTB_ERR_ARG, "MXFP8 quantise output must be e4m3 or e5m2, got dtype %d", q_dtype);
+    PTB_REQUIRE(G >= 1 && M >= 0 && N >= 0, PTB_ERR_ARG, "grouped MXFP8 quantise: at least one group, non-negative extents");
+    PTB_REQUIRE(N % kMxBlock == 0, PTB_ERR_ARG, "N (%lld) must be divisible by 32", (long long) N);
+    PTB_REQUIRE(row_align == 1 || row_align == 32, PTB_ERR_ARG, "row_align must be 1 or 32");
+    PTB_REQUIRE(group_offs && q_row && s_row && q_col && s_col && row_lens_padded && row_offs_padded && col_lens_padded &&
+                    col_offs_padded && block_table,
+                PTB_ERR_ARG, "grouped MXFP8 quantise: null pointer");
+    PTB_REQUIRE(M < (1ll << 31), PTB_ERR_TOO_LARGE, "grouped MXFP8 quantise: too many rows");
+    PTB_REQUIRE((N == 0 || aligned16(x)) && aligned16(q_row) && aligned16(q_col) && aligned16(block_table), PTB_ERR_ARG,
+                "MXFP8 quantise needs 16-byte aligned input, FP8 outputs and block table");
+    MxQuantArgs a;
+    a.x = x; a.q_row = (uint8_t *) q_row; a.s_row = (uint8_t *) s_row; a.q_col = (uint8_t *) q_col; a.s_col = (uint8_t *) s_col;
+    a.M = M; a.N = N;
+    a.M_pad = cdiv<int64_t>(M + G * kMxPad, kMxPad) * kMxPad; // rows the column layout is allocated for (upper bound)
+    a.N_pad = cdiv<int64_t>(N, kMxPad) * kMxPad;
+    a.row_2d = row_2d_block; a.col_2d = col_2d_block;
+    a.table  = (const int4 *) block_table;
+    const int64_t nblocks = a.M_pad / kMxPad;
+    PTB_REQUIRE(nblocks <= 65535, PTB_ERR_TOO_LARGE, "grouped MXFP8 quantise: more than 65535 row blocks");
+    cudaStream_t st = (cudaStream_t) stream;
+    mx_group_layout_kernel<<<1, 256, 0, st>>>(group_offs, G, row_align, row_lens_padded, row_offs_padded, col_lens_padded,
+                                              col_offs_padded, (int4 *) block_table, nblocks);
+    PTB_LAUNCH_CHECK("mx_group_layout_kernel");
+    if (N == 0) return 0;
+    dim3 grid((unsigned) (a.N_pad / 128), (unsigned) nblocks, 1);
+    if (x_dtype == PTB_BF16) {
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__nv_bfloat16, FMT, true><<<grid, 256, 0, st>>>(a)));
+    } else {
+        PTB_SWITCH_FP8(q_dtype, FMT, (mx_quant_kernel<__half, FMT, true><<<grid, 256, 0, st>>>(a)));
     }
     PTB_LAUNCH_CHECK("mx_quant_kernel");
     return 0;

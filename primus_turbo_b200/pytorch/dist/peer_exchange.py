@@ -52,27 +52,30 @@ def segment_tables(counts_matrix: torch.Tensor, rank: int) -> SegmentTables:
     """Index arithmetic of both exchanges from the host copy of the ``[world, E]`` count matrix
     (``counts_matrix[s, e]`` = rows rank ``s`` routes to expert ``e``; experts sharded contiguously,
     expert ``e`` on rank ``e // (E / world)``; every rank's rows are sorted by expert)."""
-    C = counts_matrix.to(torch.int64)
+    import numpy as np
+
+    # numpy, not torch: a dozen tiny array operations per step, and torch's dispatch costs ten times numpy's
+    C = counts_matrix.to(torch.int64).numpy()
     world, E = C.shape
     assert E % world == 0
     e_loc = E // world
     total = C.sum(0)  # rows per expert over all sources
-    blk = total.view(world, e_loc)
+    blk = total.reshape(world, e_loc)
     start_in_owner = (blk.cumsum(1) - blk).reshape(E)  # first row of expert e in its owner's buffer
     before_src = C.cumsum(0) - C  # [s, e]: rows of expert e that come from sources below s
     own_off = C.cumsum(1) - C  # [s, e]: first row of expert e in rank s's own (sorted) rows
-    experts = torch.arange(E)
-    dispatch = torch.stack(
-        [own_off[rank], start_in_owner + before_src[rank], C[rank], experts // e_loc], dim=1
-    ).contiguous()
-    mine = experts[rank * e_loc : (rank + 1) * e_loc]
+    experts = np.arange(E)
+    dispatch = np.stack([own_off[rank], start_in_owner + before_src[rank], C[rank], experts // e_loc], axis=1)
+    lo, hi = rank * e_loc, (rank + 1) * e_loc
     # (local expert, source) pairs in expert-major order
-    src_row = (start_in_owner[mine].unsqueeze(1) + before_src[:, mine].t()).reshape(-1)
-    dst_row = own_off[:, mine].t().reshape(-1)
-    rows = C[:, mine].t().reshape(-1)
-    dst_rank = torch.arange(world).repeat(e_loc)
-    combine = torch.stack([src_row, dst_row, rows, dst_rank], dim=1).contiguous()
-    return SegmentTables(dispatch, combine, total[mine].contiguous(), int(C[rank].sum()), int(total[mine].sum()))
+    src_row = (start_in_owner[lo:hi, None] + before_src[:, lo:hi].T).reshape(-1)
+    dst_row = own_off[:, lo:hi].T.reshape(-1)
+    rows = C[:, lo:hi].T.reshape(-1)
+    dst_rank = np.tile(np.arange(world), e_loc)
+    combine = np.stack([src_row, dst_row, rows, dst_rank], axis=1)
+    mine_total = np.ascontiguousarray(total[lo:hi])
+    return SegmentTables(torch.from_numpy(np.ascontiguousarray(dispatch)), torch.from_numpy(np.ascontiguousarray(combine)),
+                         torch.from_numpy(mine_total), int(C[rank].sum()), int(mine_total.sum()))
 
 
 def _device_copy(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row_bytes: int, num_ctas: int) -> None:
@@ -82,6 +85,19 @@ def _device_copy(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row
     with torch.cuda.device(src.device):
         _lib.call("ptb_copy_segments", src.data_ptr(), arr, len(dst_ptrs), segs.data_ptr(), segs.shape[0], row_bytes,
                   num_ctas, torch.cuda.current_stream(src.device).cuda_stream)
+
+
+def _device_copy_signal(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row_bytes: int, num_ctas: int,
+                        flag_slots: List[int], done_counter: int, seq: int) -> None:
+    from primus_turbo_b200 import _lib
+
+    n = len(dst_ptrs)
+    arr = (ctypes.c_void_p * n)(*dst_ptrs)
+    slots = (ctypes.c_void_p * n)(*flag_slots)
+    nseg = segs.shape[0] if src.shape[0] else 0
+    with torch.cuda.device(src.device):
+        _lib.call("ptb_copy_segments_signal", src.data_ptr() if nseg else None, arr, n, segs.data_ptr() if nseg else None,
+                  nseg, row_bytes, num_ctas, slots, done_counter, seq, torch.cuda.current_stream(src.device).cuda_stream)
 
 
 def _export_cuda_ipc(t: torch.Tensor):
@@ -115,13 +131,21 @@ class PeerExchange:
     Regions are created on first use, keyed by (direction, row width in bytes, forward / backward pass); creation is collective
     (every rank must reach it in the same order, which the symmetric call sequence of a training step
     guarantees).  ``host_group`` carries the handle exchange (a CPU group); ``group`` the ordering
-    collective (NCCL on GPUs).  ``copy_fn`` / ``alloc_fn`` replace the device pieces in CPU tests.
+    collective.  ``copy_fn`` / ``alloc_fn`` replace the device pieces in CPU tests.
+
+    Ordering after an exchange (``ordering``): ``"flags"`` (default on CUDA with the built-in copy) -- the
+    copy kernel itself stores the exchange's sequence number into this rank's slot of every destination's
+    flag array once its rows have landed, and ``order()`` enqueues a one-warp kernel that waits (with a
+    time limit) for all sources' slots; ``"collective"`` -- a one-element all-reduce on ``group``.
+    Both are a barrier among the ranks in stream order; neither blocks the host.
     """
+
+    MAX_KEYS = 32  # regions (direction x row width x pass) one exchange object can hold
 
     def __init__(self, group: Optional[dist.ProcessGroup], host_group: Optional[dist.ProcessGroup], device,
                  capacity_rows: int, local_rows: int, copy_fn: Optional[Callable] = None,
                  alloc_fn: Optional[Callable] = None, num_ctas: int = 0, export_fn: Optional[Callable] = None,
-                 import_fn: Optional[Callable] = None):
+                 import_fn: Optional[Callable] = None, ordering: Optional[str] = None):
         self.group, self.host_group = group, host_group
         self.device = torch.device(device)
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -137,6 +161,22 @@ class PeerExchange:
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         if self.device.type == "cuda" and import_fn is None:
             self._check_peer_paths()
+        if ordering is None:
+            ordering = "flags" if (self.device.type == "cuda" and copy_fn is None and import_fn is None) else "collective"
+        assert ordering in ("flags", "collective")
+        self.ordering = ordering
+        self._key_index: Dict[Tuple[str, int, str], int] = {}
+        self._seq: Dict[int, int] = {}
+        self._last: Optional[Tuple[int, int]] = None  # (key index, sequence number) of the latest push
+        if ordering == "flags":
+            # [MAX_KEYS, world] arrival slots (row k: one slot per source rank) and one CTA counter per key,
+            # zeroed; the slots are published to the other ranks like a region
+            self._flags = torch.zeros(self.MAX_KEYS * self.world + self.MAX_KEYS, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)  # the zeros are in memory before any peer may write a slot
+            handles: List = [None] * self.world
+            dist.all_gather_object(handles, self._export(self._flags), group=self.host_group)
+            self._flag_views = [self._flags if r == self.rank else self._import(h) for r, h in enumerate(handles)]
+            self._flag_ptrs = [t.data_ptr() for t in self._flag_views]
 
     def _check_peer_paths(self) -> None:
         """Before any region exists: every rank tells the others which device it runs on and enables peer
@@ -174,12 +214,29 @@ class PeerExchange:
                 views.append(t)  # keeps the mapping alive
                 ptrs.append(t.data_ptr())
             self._regions[key] = (local, views, ptrs)
+            self._key_index[key] = len(self._key_index)
+            if len(self._key_index) > self.MAX_KEYS:
+                raise RuntimeError(f"more than {self.MAX_KEYS} distinct exchange regions")
         return self._regions[key]
 
     # ---- the two exchanges ------------------------------------------------------------------------
     def order(self) -> None:
-        """Stream-ordered rendezvous of all ranks (one-element all-reduce; the host is not blocked)."""
-        dist.all_reduce(self._flag, group=self.group)
+        """Stream-ordered rendezvous of all ranks after the latest ``push`` (the host is not blocked)."""
+        if self.ordering == "flags":
+            from primus_turbo_b200 import _lib
+
+            k, seq = self._last
+            with torch.cuda.device(self.device):
+                _lib.call("ptb_wait_flags", self._flag_ptrs[self.rank] + 4 * k * self.world, self.world, seq,
+                          torch.cuda.current_stream(self.device).cuda_stream)
+            return
+        if self.device.type == "cuda":
+            from primus_turbo_b200 import _lib
+
+            with _lib.timed_region("ep_order_all_reduce"):
+                dist.all_reduce(self._flag, group=self.group)
+        else:
+            dist.all_reduce(self._flag, group=self.group)
 
     def close(self) -> None:
         """Collective teardown (call before the process group is destroyed): every rank first drops its
@@ -192,6 +249,8 @@ class PeerExchange:
             torch.cuda.synchronize(self.device)
         for key, (local, views, ptrs) in list(self._regions.items()):
             self._regions[key] = (local, [], [])
+        if self.ordering == "flags":
+            self._flag_views, self._flag_ptrs = [self._flags], []
         gc.collect()
         if self.device.type == "cuda":
             torch.cuda.ipc_collect()
@@ -214,11 +273,29 @@ class PeerExchange:
         if rows_received > limit:
             raise RuntimeError(f"{direction}: {rows_received} rows arrive at rank {self.rank} but the region holds {limit}")
         local, _, ptrs = self._region(direction, row_bytes, phase)
-        if segs.shape[0] and src.shape[0]:
+        if self.ordering == "flags":
+            # the copy runs even with nothing to send: its signal is this rank's part of the rendezvous
+            k = self._key_index[(direction, row_bytes, phase)]
+            seq = self._seq.get(k, 0) + 1
+            self._seq[k] = seq
+            self._last = (k, seq)
+            _device_copy_signal(src, ptrs, segs, row_bytes, self.num_ctas,
+                                [p + 4 * (k * self.world + self.rank) for p in self._flag_ptrs],
+                                self._flag_ptrs[self.rank] + 4 * (self.MAX_KEYS * self.world + k), seq & 0xFFFFFFFF)
+        elif segs.shape[0] and src.shape[0]:
             self._copy(src, ptrs, segs, row_bytes, self.num_ctas)
         # `.data`: a tensor over the same bytes with its own version counter -- the region is rewritten by
         # later exchanges (by kernels of other ranks), which autograd must not mistake for an in-place edit
         return local.data[: rows_received * row_bytes].view(src.dtype).view(rows_received, src.shape[1])
+
+
+def _copy_out(region_view: torch.Tensor) -> torch.Tensor:
+    if region_view.is_cuda:
+        from primus_turbo_b200 import _lib
+
+        with _lib.timed_region("ep_copy_out_of_region"):
+            return region_view.clone()
+    return region_view.clone()
 
 
 class _PeerMove(torch.autograd.Function):
@@ -232,14 +309,14 @@ class _PeerMove(torch.autograd.Function):
         ctx.bwd_direction = "combine" if direction == "dispatch" else "dispatch"
         out = ex.push(x.contiguous(), fwd_segs, direction, rows_fwd)
         ex.order()
-        return out.clone() if direction == "combine" else out
+        return _copy_out(out) if direction == "combine" else out
 
     @staticmethod
     def backward(ctx, g):
         ex = ctx.ex
         out = ex.push(g.contiguous(), ctx.bwd_segs, ctx.bwd_direction, ctx.rows_bwd, phase="bwd")
         ex.order()
-        return (out.clone() if ctx.bwd_direction == "combine" else out), None, None, None, None, None, None
+        return (_copy_out(out) if ctx.bwd_direction == "combine" else out), None, None, None, None, None, None
 
 
 def peer_dispatch(x_local: torch.Tensor, ex: PeerExchange, tables: SegmentTables, seg_dev: Tuple[torch.Tensor, torch.Tensor]):

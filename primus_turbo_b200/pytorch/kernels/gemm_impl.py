@@ -128,6 +128,49 @@ def gemm_mxfp8_impl(
     return out
 
 
+def grouped_gemm_mxfp8_impl(
+    a: torch.Tensor, a_scale_inv: torch.Tensor, b: torch.Tensor, b_scale_inv: torch.Tensor, group_offs: torch.Tensor,
+    out_dtype: torch.dtype, num_sms: int = 0,
+) -> torch.Tensor:
+    """out[rows of group g] = a[rows of group g] . b[g]^T: a [M, K_pad] with scale bytes [M, K_pad/32] (rows at
+    their unpadded positions), b [G, N, K_pad] with [G, N, K_pad/32]; rows at or past group_offs[G] are zero."""
+    require_cuda(a, b, a_scale_inv, b_scale_inv, group_offs)
+    assert a.dim() == 2 and b.dim() == 3 and a.shape[1] == b.shape[2]
+    a, b = _as_rows(a), b.contiguous()
+    a_s, b_s = a_scale_inv.view(torch.uint8), b_scale_inv.view(torch.uint8).contiguous()
+    m, k = a.shape
+    g, n = b.shape[0], b.shape[1]
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.call(
+            "ptb_grouped_gemm_mxfp8", ptr(a), dtype_code(a.dtype), a.stride(0), ptr(a_s), a_s.stride(0), ptr(b),
+            dtype_code(b.dtype), ptr(b_s), ptr(out), dtype_code(out_dtype), out.stride(0), ptr(group_offs), g, m, n, k,
+            num_sms, stream_of(a),
+        )
+    return out
+
+
+def grouped_gemm_mxfp8_variable_k_impl(
+    lhs: torch.Tensor, lhs_scale_inv: torch.Tensor, rhs: torch.Tensor, rhs_scale_inv: torch.Tensor,
+    group_offs_padded: torch.Tensor, out_dtype: torch.dtype, num_sms: int = 0,
+) -> torch.Tensor:
+    """out[g] = lhs[:, cols of g] . rhs[:, cols of g]^T for the transposed column copies lhs [OUT_M, rows_padded],
+    rhs [OUT_N, rows_padded] of the grouped quantiser; -> [G, OUT_M, OUT_N]."""
+    require_cuda(lhs, rhs, lhs_scale_inv, rhs_scale_inv, group_offs_padded)
+    assert lhs.dim() == 2 and rhs.dim() == 2 and lhs.shape[1] == rhs.shape[1]
+    lhs, rhs = _as_rows(lhs), _as_rows(rhs)
+    l_s, r_s = lhs_scale_inv.view(torch.uint8), rhs_scale_inv.view(torch.uint8)
+    g = group_offs_padded.numel() - 1
+    out = torch.empty((g, lhs.shape[0], rhs.shape[0]), dtype=out_dtype, device=lhs.device)
+    with torch.cuda.device(lhs.device):
+        _lib.call(
+            "ptb_grouped_gemm_mxfp8_variable_k", ptr(lhs), dtype_code(lhs.dtype), lhs.stride(0), ptr(l_s), l_s.stride(0),
+            ptr(rhs), dtype_code(rhs.dtype), rhs.stride(0), ptr(r_s), r_s.stride(0), ptr(out), dtype_code(out_dtype),
+            ptr(group_offs_padded), g, lhs.shape[1], lhs.shape[0], rhs.shape[0], num_sms, stream_of(lhs),
+        )
+    return out
+
+
 def group_offs_from_lens(group_lens: torch.Tensor) -> torch.Tensor:
     """Exclusive prefix sum on the device (grouped_gemm_utils.py:28-34)."""
     assert group_lens.is_cuda, "group_lens must be on CUDA"

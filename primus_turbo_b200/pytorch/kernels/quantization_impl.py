@@ -367,3 +367,50 @@ def dequantize_mxfp8_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int, bl
                     dtype_code(out_dtype), stream_of(x),
                 )
     return out
+
+
+def grouped_quantize_mxfp8_impl(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    block_size: int,
+    group_lens: torch.Tensor,
+    group_offs: torch.Tensor,
+    use_2d_block: bool = False,
+    use_2d_block_for_trans: bool = False,
+    row_align: int = 32,
+):
+    """x [M, N] whose rows form ``len(group_lens)`` groups -> (q_row, s_row, q_col_t, s_col, row_lens_padded,
+    row_offs_padded, col_lens_padded, col_offs_padded): every group quantised on its own, padded to
+    ``row_align`` rows in the row copy (32: the reference's layout; 1: no padding, what this build's grouped
+    GEMM reads) and to 128 rows in the transposed column copy.  Nothing synchronises with the host; the
+    outputs are allocated for the worst case.  Rows of the row copy that hold no group row are unspecified
+    (the reference leaves them unwritten as well).
+    (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:546-599,
+    csrc/pytorch/quantization/quantization.cpp:1075-1195 in the reference.)"""
+    require_cuda(x, group_lens, group_offs)
+    assert block_size == MX_BLOCK, f"The block size must be {MX_BLOCK} for MXFP8 quantization"
+    assert x.dtype in (torch.bfloat16, torch.float16), "Input must be BFloat16 or Half"
+    assert x.dim() == 2 and x.is_contiguous(), "Input must be 2D and contiguous"
+    assert group_lens.dtype == torch.int64 and group_offs.dtype == torch.int64, "group_lens / group_offs must be int64"
+    assert group_offs.numel() == group_lens.numel() + 1 and group_lens.numel() >= 1
+    M, N = x.shape
+    G = group_lens.numel()
+    assert N % MX_BLOCK == 0, f"N must be divisible by {MX_BLOCK}"
+    N_pad = ceil_div(N, MX_PAD) * MX_PAD
+    M_row = ceil_div(M + G * row_align, row_align) * row_align if row_align > 1 else M
+    M_col = ceil_div(M + G * MX_PAD, MX_PAD) * MX_PAD
+    dev = x.device
+    q_row = torch.empty((M_row, N_pad), dtype=out_dtype, device=dev)
+    s_row = torch.empty((M_row, N_pad // MX_BLOCK), dtype=torch.uint8, device=dev)
+    q_col = torch.empty((N, M_col), dtype=out_dtype, device=dev)
+    s_col = torch.empty((N, M_col // MX_BLOCK), dtype=torch.uint8, device=dev)
+    layout = torch.empty(4 * G + 2, dtype=torch.int64, device=dev)
+    row_lens, row_offs, col_lens, col_offs = layout[:G], layout[G : 2 * G + 1], layout[2 * G + 1 : 3 * G + 1], layout[3 * G + 1 :]
+    table = torch.empty(M_col // MX_PAD * 4, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call(
+            "ptb_quant_mxfp8_grouped", ptr(x), dtype_code(x.dtype), M, N, ptr(group_offs.contiguous()), G, row_align, ptr(q_row),
+            ptr(s_row), ptr(q_col), ptr(s_col), ptr(row_lens), ptr(row_offs), ptr(col_lens), ptr(col_offs), ptr(table),
+            int(use_2d_block), int(use_2d_block_for_trans), dtype_code(out_dtype), stream_of(x),
+        )
+    return q_row, s_row.view(E8M0), q_col, s_col.view(E8M0), row_lens, row_offs, col_lens, col_offs

@@ -35,7 +35,12 @@ from primus_turbo_b200.pytorch.kernels.custom_ops import quant_fp8_blockwise_for
 from primus_turbo_b200.pytorch.kernels.custom_ops import (
     quant_fp8_blockwise_segment_m_row_col as quant_fp8_blockwise_segment_m_row_col_impl,
 )
-from primus_turbo_b200.pytorch.kernels.gemm_impl import group_offs_from_lens
+from primus_turbo_b200.pytorch.kernels.gemm_impl import (
+    group_offs_from_lens,
+    grouped_gemm_mxfp8_impl,
+    grouped_gemm_mxfp8_variable_k_impl,
+)
+from primus_turbo_b200.pytorch.kernels.quantization_impl import grouped_quantize_mxfp8_impl, quantize_mxfp8_impl
 
 __all__ = ["grouped_gemm_fp8"]
 
@@ -213,6 +218,47 @@ class FP8GroupedGemmTensorFunc(torch.autograd.Function):
 
 
 @torch._dynamo.disable(recursive=True, reason="builds QuantizedTensor wrappers inside autograd.Function.forward")
+class FP8GroupedGemmMXFunc(torch.autograd.Function):
+    """MX_BLOCKWISE grouped GEMM (primus_turbo/pytorch/ops/grouped_gemm_fp8.py:571-795): a and grad_out are
+    quantised per group in both directions in one pass, b per expert in both directions (32x32 tiles);
+    forward and dgrad read the row copies, wgrad the transposed column copies over each group's 128-padded
+    row range.  The reference's forward reads a row copy padded to 32 rows per group and writes a packed
+    output; 1x32 blocks along K do not depend on the padding, so this build keeps the row copy unpadded
+    and the numbers are the same."""
+
+    @staticmethod
+    def forward(ctx, a, b, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+        assert config.granularity == ScalingGranularity.MX_BLOCKWISE
+        assert a.ndim == 2 and b.ndim == 3
+        assert trans_b, "MXFP8 grouped GEMM only supports trans_b=True (NT layout)."
+        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
+            raise NotImplementedError("MX_BLOCKWISE grouped_gemm_fp8 takes high-precision tensors in this build")
+        dt = _get_fp8_dtype(config.format, True)
+        a_row, a_row_s, a_col, a_col_s, _, _, _, col_offs = grouped_quantize_mxfp8_impl(
+            _contig(a), dt, config.block_size, group_lens, group_offs, False, False, row_align=1
+        )
+        b_row, b_row_s, b_col, b_col_s = quantize_mxfp8_impl(_contig(b), dt, None, config.block_size, True, True, True)
+        sms = num_cu or 0
+        out = grouped_gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, group_offs, out_dtype, sms)
+        ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s, group_lens, group_offs)
+        ctx.config, ctx.out_dtype, ctx.sms = config, out_dtype, sms
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        a_col, a_col_s, b_col, b_col_s, group_lens, group_offs = ctx.saved_tensors
+        cfg = ctx.config
+        g_row, g_row_s, g_col, g_col_s, _, _, _, col_offs = grouped_quantize_mxfp8_impl(
+            _contig(grad_out), _get_fp8_dtype(cfg.format, False), cfg.block_size, group_lens, group_offs, False, False,
+            row_align=1,
+        )
+        # dgrad: grad_a = grad_out . b   = [M, N_pad] x (b_col [G, K, N_pad])^T
+        grad_a = grouped_gemm_mxfp8_impl(g_row, g_row_s, b_col, b_col_s, group_offs, ctx.out_dtype, ctx.sms)
+        # wgrad: grad_b[g] = grad_out_g^T . a_g = g_col [N, rows] x (a_col [K, rows])^T over the group's padded rows
+        grad_b = grouped_gemm_mxfp8_variable_k_impl(g_col, g_col_s, a_col, a_col_s, col_offs, ctx.out_dtype, ctx.sms)
+        return grad_a, grad_b, None, None, None, None, None, None
+
+
 def grouped_gemm_fp8(
     a: Union[torch.Tensor, QuantizedTensor, QuantizedTensorPair],
     b: Union[torch.Tensor, QuantizedTensor, QuantizedTensorPair],
@@ -249,4 +295,6 @@ def grouped_gemm_fp8(
         # raw activations; the weight may be raw or pre-quantised (the pair's forward member: forward
         # and dgrad read the same 128x128-block payload)
         return FP8GroupedGemmBlockFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
+    if config.granularity == ScalingGranularity.MX_BLOCKWISE:
+        return FP8GroupedGemmMXFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

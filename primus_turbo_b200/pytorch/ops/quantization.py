@@ -9,9 +9,13 @@ import torch
 from primus_turbo_b200.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
 from primus_turbo_b200.pytorch.core.low_precision import MXFP8_BLOCK_SIZE
 from primus_turbo_b200.pytorch.kernels import custom_ops as _ops
-from primus_turbo_b200.pytorch.kernels.quantization_impl import dequantize_mxfp8_impl, quantize_mxfp8_impl
+from primus_turbo_b200.pytorch.kernels.quantization_impl import (
+    dequantize_mxfp8_impl,
+    grouped_quantize_mxfp8_impl,
+    quantize_mxfp8_impl,
+)
 
-__all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8"]
+__all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8", "grouped_quantize_fp8_with_trans"]
 
 
 def quantize_fp8(
@@ -79,6 +83,33 @@ def quantize_fp8_with_trans(
         _reject_shuffle(scaling_recipe_for_trans)
         return quantize_mxfp8_impl(
             x, out_dtype, None, block_size, True,
+            bool(scaling_recipe is not None and scaling_recipe.use_2d_block),
+            bool(scaling_recipe_for_trans is not None and scaling_recipe_for_trans.use_2d_block),
+        )
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_quantize_fp8_with_trans(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    group_lens: torch.Tensor,
+    group_offs: torch.Tensor,
+    *,
+    block_size: Optional[int] = None,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+    scaling_recipe_for_trans: Optional[ScalingRecipe] = None,
+):
+    """MXFP8 only (as in the reference, ops/quantization.py:181-222): both directions of x [M, N] per group;
+    -> (x_rowwise, scale_rowwise, x_colwise_t, scale_colwise, group_lens_padded_rowwise,
+    group_offs_padded_rowwise, group_lens_padded_colwise, group_offs_padded_colwise).  The row copy pads every
+    group to 32 rows, the transposed column copy to 128."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        _reject_shuffle(scaling_recipe)
+        _reject_shuffle(scaling_recipe_for_trans)
+        return grouped_quantize_mxfp8_impl(
+            x, out_dtype, block_size, group_lens, group_offs,
             bool(scaling_recipe is not None and scaling_recipe.use_2d_block),
             bool(scaling_recipe_for_trans is not None and scaling_recipe_for_trans.use_2d_block),
         )

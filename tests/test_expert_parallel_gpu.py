@@ -43,7 +43,7 @@ def _worker(rank, store_path, q, overlap, WORLD):
         e_loc = E // WORLD
         x = xs[rank].cuda().requires_grad_(True)
         w_loc = w[rank * e_loc : (rank + 1) * e_loc].cuda().requires_grad_(True)
-        if overlap == "peer":
+        if overlap in ("peer", "peer-collective"):
             # rows written straight into the owners' IPC-mapped buffers, two steps (regions are reused)
             from primus_turbo_b200.pytorch.dist.expert_parallel import build_peer_plan, expert_parallel_apply_peer
             from primus_turbo_b200.pytorch.dist.peer_exchange import PeerExchange
@@ -51,7 +51,9 @@ def _worker(rank, store_path, q, overlap, WORLD):
 
             host_group = dist.new_group(backend="gloo")
             ex = PeerExchange(None, host_group, torch.device("cuda", rank), capacity_rows=int(counts.sum()),
-                              local_rows=int(counts.sum(1).max()))
+                              local_rows=int(counts.sum(1).max()),
+                              ordering="collective" if overlap == "peer-collective" else None)
+            assert ex.ordering == ("collective" if overlap == "peer-collective" else "flags")
             for _ in range(2):
                 x.grad = w_loc.grad = None
                 plan = build_peer_plan(counts[rank], host_group, torch.device("cuda", rank))
@@ -68,7 +70,7 @@ def _worker(rank, store_path, q, overlap, WORLD):
             torch.cuda.synchronize()
         q.put((rank, out.detach().float().cpu().tolist(), x.grad.float().cpu().tolist(), w_loc.grad.float().cpu().tolist()))
         dist.barrier()
-        if overlap == "peer":
+        if overlap in ("peer", "peer-collective"):
             ex.close()
     except Exception as exc:
         q.put((rank, repr(exc), None, None))
@@ -77,7 +79,7 @@ def _worker(rank, store_path, q, overlap, WORLD):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("overlap", [False, True, "peer"])
+@pytest.mark.parametrize("overlap", [False, True, "peer", "peer-collective"])
 @pytest.mark.parametrize("WORLD", [2, 4, 8])
 def test_expert_parallel_matches_single_gpu(overlap, WORLD):
     if torch.cuda.device_count() < WORLD:

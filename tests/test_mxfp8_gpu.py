@@ -143,3 +143,84 @@ def test_argument_checks():
     with pytest.raises(NotImplementedError):
         quantize_fp8(x[:, :32].contiguous(), torch.float8_e4m3fn, MX, block_size=32, axis=1,
                      scaling_recipe=ScalingRecipe(shuffle_scale=True))
+
+
+# ---- grouped forms ------------------------------------------------------------------------------------------
+from primus_turbo_b200.pytorch.kernels.quantization_impl import grouped_quantize_mxfp8_impl  # noqa: E402
+from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8  # noqa: E402
+from primus_turbo_b200.pytorch.ops.quantization import grouped_quantize_fp8_with_trans  # noqa: E402
+
+GROUPS = [[100, 0, 157, 43], [1], [128, 256, 384], [0, 0, 5], [33, 31, 32, 129, 1, 64]]
+
+
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("lens", GROUPS)
+@pytest.mark.parametrize("use_2d", [False, True])
+@pytest.mark.parametrize("row_align", [32, 1])
+def test_grouped_quantize_matches_oracle(fp8, lens, use_2d, row_align):
+    M, N = sum(lens), 96
+    x = _mk((M, N), torch.bfloat16, seed=M)
+    if M > 40:
+        x[35:40] = 0  # a zero block inside a group: scale byte 127 in the grouped kernels
+    gl = torch.tensor(lens, dtype=torch.int64)
+    go = torch.cat([gl.new_zeros(1), gl.cumsum(0)])
+    got = grouped_quantize_mxfp8_impl(x.to(DEV), fp8, 32, gl.to(DEV), go.to(DEV), use_2d, use_2d, row_align=row_align)
+    q_row, s_row, q_col, s_col, row_lens, row_offs, col_lens, col_offs = got
+    rq, rs, cq, cs, r_offs, c_offs, written = O.quant_mxfp8_grouped(x, fp8, go.tolist(), row_align, use_2d)
+    assert row_offs.cpu().tolist() == r_offs and col_offs.cpu().tolist() == c_offs
+    assert row_lens.cpu().tolist() == [b - a for a, b in zip(r_offs[:-1], r_offs[1:])]
+    assert col_lens.cpu().tolist() == [b - a for a, b in zip(c_offs[:-1], c_offs[1:])]
+    assert q_row.shape == rq.shape and s_row.shape == rs.shape and q_col.shape == cq.shape and s_col.shape == cs.shape
+    w = written
+    assert torch.equal(q_row.cpu().view(torch.uint8)[w], rq.view(torch.uint8)[w]), "row FP8 bytes"
+    assert torch.equal(s_row.cpu().view(torch.uint8)[w], rs[w]), "row scale bytes"
+    assert _same_bytes(q_col, cq), "column FP8 bytes"
+    assert _same_bytes(s_col, cs), "column scale bytes"
+
+
+def test_grouped_quantize_public_op_uses_the_reference_layout():
+    lens = [40, 70]
+    x = _mk((110, 64), torch.bfloat16, seed=9).to(DEV)
+    gl = torch.tensor(lens, dtype=torch.int64, device=DEV)
+    go = torch.cat([gl.new_zeros(1), gl.cumsum(0)])
+    out = grouped_quantize_fp8_with_trans(x, torch.float8_e4m3fn, MX, gl, go, block_size=32)
+    assert len(out) == 8
+    assert out[0].shape == (192, 128) and out[2].shape == (64, 384)  # ceil((110 + 2*32)/32)*32, ceil((110 + 2*128)/128)*128
+    assert out[5].cpu().tolist() == [0, 64, 160] and out[7].cpu().tolist() == [0, 128, 256]
+
+
+@pytest.mark.parametrize("fmt", [Format.E4M3, Format.HYBRID])
+@pytest.mark.parametrize("lens", [[100, 0, 157, 43], [128, 256, 384], [1, 0, 5, 300, 77, 33], [512] * 8])
+@pytest.mark.parametrize("NK", [(256, 128), (320, 96), (1024, 1024)])
+def test_grouped_gemm_forward_backward_vs_oracle(fmt, lens, NK):
+    N, K = NK
+    G, M = len(lens), sum(lens)
+    cfg = Float8QuantConfig(format=fmt, granularity=MX, block_size=32, scale_dtype=ScaleDtype.E8M0)
+    a = _mk((M, K), torch.bfloat16, seed=1)
+    b = _mk((G, N, K), torch.bfloat16, seed=2, scale=0.05)
+    gy = _mk((M, N), torch.bfloat16, seed=3, scale=0.01)
+    gl = torch.tensor(lens, dtype=torch.int64)
+    go = torch.cat([gl.new_zeros(1), gl.cumsum(0)]).tolist()
+    ad, bd = a.to(DEV).requires_grad_(), b.to(DEV).requires_grad_()
+    out = grouped_gemm_fp8(ad, bd, gl.to(DEV), trans_b=True, config=cfg)
+    out.backward(gy.to(DEV))
+    out = out.detach()
+    fwd = torch.float8_e4m3fn
+    bwd = torch.float8_e4m3fn if fmt == Format.E4M3 else torch.float8_e5m2
+    a_row, a_rs, a_col, a_cs, _, c_offs, _ = O.quant_mxfp8_grouped(a, fwd, go, 1)
+    g_row, g_rs, g_col, g_cs, _, _, _ = O.quant_mxfp8_grouped(gy, bwd, go, 1)
+    b_row = [O.quant_mxfp8(b[g], fwd, 1, True) for g in range(G)]
+    b_col = [O.quant_mxfp8(b[g], fwd, 0, True) for g in range(G)]
+    stack = lambda pairs, i: torch.stack([p[i] for p in pairs])  # noqa: E731
+    ref_out = O.grouped_gemm_mxfp8(a_row, a_rs, stack(b_row, 0), stack(b_row, 1), go)
+    ref_ga = O.grouped_gemm_mxfp8(g_row, g_rs, stack(b_col, 0), stack(b_col, 1), go)
+    ref_gb = O.grouped_gemm_mxfp8_variable_k(g_col, g_cs, a_col, a_cs, c_offs)
+    assert out.shape == (M, N) and ad.grad.shape == (M, K) and bd.grad.shape == (G, N, K)
+    assert O.rel_frobenius(ref_out, out.cpu()) <= 1e-2
+    assert O.rel_frobenius(ref_ga, ad.grad.cpu()) <= 1e-2
+    assert O.rel_frobenius(ref_gb, bd.grad.cpu()) <= 1e-2
+    for g in range(G):  # an empty group's weight gradient is exactly zero
+        if lens[g] == 0:
+            assert bd.grad[g].abs().max().item() == 0.0
+    hp = torch.cat([a[go[g] : go[g + 1]].float() @ b[g].float().t() for g in range(G)])
+    assert O.snr_db(hp, out.float().cpu()) > 25
