@@ -401,27 +401,40 @@ def _finish_line(args, line, kernel_ms, roofs, clocks, launches, status):
     print(json.dumps(line), flush=True)
 
 
+LOG_PASS_STEPS = [None]  # steps of the separate event-logging pass (None: events were taken in the timed steps)
 HOST_ENQUEUE_MS = [None]  # set by _timed: when it nears ms_per_step the host, not the GPU, paces the step
 
 
-def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None):
-    """(ms per step, per-entry-point kernel times, clock summary, launches)"""
+def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None, log_pass=False):
+    """(ms per step, per-entry-point kernel times, clock summary, launches).
+
+    log_pass: take the per-call CUDA events in a separate pass of up to three steps right after the timed
+    steps instead of inside them.  A multi-GPU step is short enough for the host to pace it, and two event
+    records around each of its ~40 calls are host time the timed region should not carry; on one GPU the
+    device paces the step and the events stay inside the timed region."""
+    import contextlib
+    import gc
+
     from primus_turbo_b200 import _lib
 
     for _ in range(max(warmup, 3)):
         step(*inputs)
     barrier()
     launches0 = _lib.launch_count
-    with ClockSampler(device_index) as clocks, _lib.record_kernel_times() as rec:
+    with ClockSampler(device_index) as clocks, (contextlib.nullcontext() if log_pass else _lib.record_kernel_times()) as rec:
         barrier()
         if flush is None:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            gc_was = gc.isenabled()
+            gc.disable()  # no collector pause in the middle of a step
             ev0.record()
             h0 = time.perf_counter()
             for _ in range(steps):
                 step(*inputs)
             HOST_ENQUEUE_MS[0] = (time.perf_counter() - h0) * 1e3 / steps  # host time to enqueue one step
             ev1.record()
+            if gc_was:
+                gc.enable()
             barrier()
             ms = ev0.elapsed_time(ev1) / steps
         else:
@@ -435,7 +448,15 @@ def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None):
                 evs.append((e0, e1))
             barrier()
             ms = sum(a.elapsed_time(b) for a, b in evs) / steps
-    return ms, rec.durations_ms(), clocks.summary(), _lib.launch_count - launches0
+    launches = _lib.launch_count - launches0
+    if log_pass:
+        n_log = min(steps, 3)
+        with _lib.record_kernel_times() as rec:
+            for _ in range(n_log):
+                step(*inputs)
+            barrier()
+        LOG_PASS_STEPS[0] = n_log
+    return ms, rec.durations_ms(), clocks.summary(), launches
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -687,8 +708,11 @@ def run_grouped(args):
 
     # ---- device-resident timing ---------------------------------------------------------------------------
     plan_ms.clear()
-    ms, kernel_ms, clocks, launches = _timed(step, (a, gy), args.steps, args.warmup, barrier, local_rank)
-    plan_host_ms = statistics.mean(plan_ms[-args.steps:]) if plan_ms else 0.0
+    ms, kernel_ms, clocks, launches = _timed(step, (a, gy), args.steps, args.warmup, barrier, local_rank, log_pass=world > 1)
+    k_steps = LOG_PASS_STEPS[0] or args.steps  # steps the per-call event log covers
+    n_log = LOG_PASS_STEPS[0] or 0
+    timed_plans = plan_ms[len(plan_ms) - n_log - args.steps: len(plan_ms) - n_log]
+    plan_host_ms = statistics.mean(timed_plans) if timed_plans else 0.0
     host_enqueue_ms = HOST_ENQUEUE_MS[0]
     status = _lib.gemm_status()
     copy_status = _lib.copy_segments_status() if state["exchange"] is not None else 0
@@ -764,10 +788,10 @@ def run_grouped(args):
                       "achieved": sent * (world - 1) / world / (r["avg_launch_ms"] * 1e-3) / 1e9})
             r["frac"] = r["achieved"] / r["peak"]
             roofs.append(r)
-        other_ms = {k: sum(kernel_ms.pop(k)) / args.steps for k in list(kernel_ms) if k.startswith("ep_")}
-        step_kernels = sum(sum(v) for v in kernel_ms.values()) / args.steps
-        copy_k = sum(kernel_ms.get(copy_key, [])) / args.steps
-        wait_k = sum(kernel_ms.get("ptb_wait_flags", [])) / args.steps
+        other_ms = {k: sum(kernel_ms.pop(k)) / k_steps for k in list(kernel_ms) if k.startswith("ep_")}
+        step_kernels = sum(sum(v) for v in kernel_ms.values()) / k_steps
+        copy_k = sum(kernel_ms.get(copy_key, [])) / k_steps
+        wait_k = sum(kernel_ms.get("ptb_wait_flags", [])) / k_steps
         wl = _workload_config(args.config)
         wl.update({"experts": E, "routed_rows": ROWS, "experts_per_gpu": e_loc, "parallelism": f"ep{world}",
                    "exchange": (args.exchange if world > 1 else None), "placement": (args.placement if world > 1 else None),
@@ -799,6 +823,9 @@ def run_grouped(args):
                                  "ordering": other_ms.get("ep_order_all_reduce", wait_k),
                                  "copies_out_of_regions": other_ms.get("ep_copy_out_of_region"),
                                  "not_in_kernels": ms - step_kernels,
+                                 "kernel_times_from": (f"a logging pass of {LOG_PASS_STEPS[0]} steps right after the timed "
+                                                       "steps (per-call events are host time a multi-GPU step "
+                                                       "cannot hide)" if LOG_PASS_STEPS[0] else "the timed steps"),
                                  "note": "rank 0's kernels; plan_host is host time that overlaps the device queue; "
                                          "ordering (flag waits or all-reduces) includes waiting for the slowest rank; "
                                          "not_in_kernels covers collectives, torch's copies and launch gaps"}
