@@ -705,6 +705,21 @@ def run_grouped(args):
         nz = torch.nonzero(pos_counts > 0).flatten().tolist()
         sample = sorted({nz[0], nz[len(nz) // 3], nz[(2 * len(nz)) // 3], nz[-1]})
         ep_parity = _ep_parity(dist, rank, world, dev, cfg, qcfg, counts_here, a, gy, w, step, sample)
+        flags_status = _lib.copy_segments_status(reset=False) if state["exchange"] is not None else 0
+        st = torch.tensor([flags_status], device=dev, dtype=torch.int32)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        if state["exchange"] is not None and state["exchange"].ordering == "flags" and (not ep_parity or int(st.item()) != 0):
+            # the flag rendezvous did not give the single-GPU results on this machine: measure with the
+            # collective instead and say so (every rank takes this branch: both inputs are reduced values)
+            print(f"[bench] rank {rank}: flag ordering failed its check (parity {ep_parity}, status {int(st.item())}); "
+                  "using the all-reduce ordering", file=sys.stderr)
+            _lib.copy_segments_status(reset=True)
+            state["exchange"].close()
+            args.ep_ordering = "collective (flags failed their check)"
+            exchange = PeerExchange(None, host_group, dev, capacity_rows=cap, local_rows=rows_here, num_ctas=args.copy_ctas,
+                                    ordering="collective")
+            state["exchange"] = exchange
+            ep_parity = _ep_parity(dist, rank, world, dev, cfg, qcfg, counts_here, a, gy, w, step, sample)
 
     # ---- device-resident timing ---------------------------------------------------------------------------
     plan_ms.clear()
