@@ -47,7 +47,7 @@ sys.path.insert(0, str(REPO))
 
 METRIC = {"c1": "blockwise_fp8_quantize_gemm_throughput", "c2": "tensorwise_fp8_gemm_throughput",
           "c3": "rowwise_fp8_gemm_fwd_dgrad_wgrad_throughput", "c4": "blockwise_fp8_grouped_gemm_throughput",
-          "c5": "blockwise_fp8_grouped_gemm_throughput"}
+          "c5": "blockwise_fp8_grouped_gemm_throughput", "mx": "mxfp8_gemm_fwd_dgrad_wgrad_throughput"}
 UNIT = "TFLOP/s"
 GROUPED = {
     "c4": dict(E=256, K=7168, N=4096, ROWS=65536, counts="softmax",
@@ -62,6 +62,9 @@ DENSE = {
                workload="llama3_8b_mlp_up_tensorwise_fp8_gemm_fwd"),
     "c3": dict(M=16384, N=8192, K=8192, gran="rowwise", bwd=True, w_scale=0.02,
                workload="llama3_70b_attn_out_rowwise_fp8_gemm_fwd_dgrad_wgrad"),
+    # not a BASELINE.json configuration: the c3 shape in the MXFP8 format (1x32 blocks, E8M0 scales)
+    "mx": dict(M=16384, N=8192, K=8192, gran="mx", bwd=True, w_scale=0.02,
+               workload="llama3_70b_attn_out_mxfp8_gemm_fwd_dgrad_wgrad"),
 }
 
 
@@ -223,6 +226,15 @@ def _cpu_dense_sample(cfg):
             aq, a_s, _, _ = O.quant_block1d_dual(x, E4)
             bq, b_s = O.quant_block2d(w, E4)
             return O.gemm_blockwise_nt(aq, a_s, bq, b_s, torch.bfloat16)
+        if cfg["gran"] == "mx":
+            a_row, a_rs = O.quant_mxfp8(x, E4, 1)
+            a_col, a_cs = O.quant_mxfp8(x, E4, 0)
+            b_row, b_rs = O.quant_mxfp8(w, E4, 1, True)
+            b_col, b_cs = O.quant_mxfp8(w, E4, 0, True)
+            g_row, g_rs = O.quant_mxfp8(gy, E4, 1)
+            g_col, g_cs = O.quant_mxfp8(gy, E4, 0)
+            return (O.gemm_mxfp8_nt(a_row, a_rs, b_row, b_rs), O.gemm_mxfp8_nt(g_row, g_rs, b_col, b_cs),
+                    O.gemm_mxfp8_nt(g_col, g_cs, a_col, a_cs))
         if cfg["gran"] == "tensorwise":
             aq, a_s = O.quant_tensorwise(x, E4)
             bq, b_s = O.quant_tensorwise(w, E4)
@@ -464,7 +476,7 @@ def _timed(step, inputs, steps, warmup, barrier, device_index, flush=None, log_p
 # ---------------------------------------------------------------------------------------------------
 def run_dense(args):
     from primus_turbo_b200 import _lib
-    from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity
+    from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScaleDtype, ScalingGranularity
     from primus_turbo_b200.pytorch.ops import gemm_fp8
 
     assert args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1, "the dense configurations run on one GPU"
@@ -473,8 +485,11 @@ def run_dense(args):
     torch.cuda.set_device(dev)
     M, N, K = cfg["M"], cfg["N"], cfg["K"]
     gran = {"blockwise": ScalingGranularity.BLOCKWISE, "tensorwise": ScalingGranularity.TENSORWISE,
-            "rowwise": ScalingGranularity.ROWWISE}[cfg["gran"]]
-    qcfg = Float8QuantConfig(granularity=gran, block_size=128 if cfg["gran"] == "blockwise" else None)
+            "rowwise": ScalingGranularity.ROWWISE, "mx": ScalingGranularity.MX_BLOCKWISE}[cfg["gran"]]
+    if cfg["gran"] == "mx":
+        qcfg = Float8QuantConfig(granularity=gran, block_size=32, scale_dtype=ScaleDtype.E8M0)
+    else:
+        qcfg = Float8QuantConfig(granularity=gran, block_size=128 if cfg["gran"] == "blockwise" else None)
     g = torch.Generator().manual_seed(0)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
     w = (torch.randn(N, K, generator=g) * cfg["w_scale"]).to(torch.bfloat16).to(dev).requires_grad_(cfg["bwd"])
@@ -512,16 +527,20 @@ def run_dense(args):
                        "copy_only_ms_per_step is the same traffic with no kernels in between (the PCIe ceiling)"}
     peaks = _peaks()
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-    gemm_t = kernel_ms.get("ptb_gemm_fp8", [])
+    gemm_name = "ptb_gemm_mxfp8" if cfg["gran"] == "mx" else "ptb_gemm_fp8"
+    gemm_t = kernel_ms.get(gemm_name, [])
     per_gemm = 2 * M * N * K
     op_bytes = M * K + N * K + M * N * 2  # fp8 operands in, bf16 out (forward shape; dgrad / wgrad permute M, N, K)
-    roofs = [_roof("ptb_gemm_fp8", f"fp8_gemm_kernel<{cfg['gran']}, bf16> (dense, {gemms} launch(es) per step)", per_gemm,
+    roofs = [_roof(gemm_name, f"fp8_gemm_kernel<{cfg['gran']}, bf16> (dense, {gemms} launch(es) per step)", per_gemm,
                    op_bytes, gemm_t, peaks, fp8_peak)]
     for name, v in kernel_ms.items():
         if name.startswith("ptb_quant") and v:
             n_el = {"ptb_quant_fp8_block2d": N * K}.get(name, M * max(K, N) if cfg["bwd"] else M * K)
+            per_el = 4.0625 if name == "ptb_quant_mxfp8" else 3.03  # both directions in one pass: 2 R + 2 W + 2/32
+            if name == "ptb_quant_mxfp8":
+                n_el = (M * K + N * K + M * N) / 3.0  # mean over the step's three calls (x, w, grad-out)
             roofs.append(_roof(name, "quantise kernel(s) of this entry point (bytes of the largest operand it sees)", 0,
-                               n_el * 3.03, v, peaks, fp8_peak))
+                               n_el * per_el, v, peaks, fp8_peak))
     value = flops / (ms * 1e-3) / 1e12
     wl = _workload_config(args.config)
     wl["l2"] = ("L2 flushed (256 MiB memset) between timed iterations" if flush is not None

@@ -595,8 +595,8 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 }
             }
             if (!ok && lane == 0) atomicExch(&g_gemm_status, 2);
-        } else if (warp == 3) {
-            // ================= scale loader (1-D x 1-D block scales) =================
+        } else if (warp == 3 || (SCALE == kScaleMX && warp == 2)) {
+            // ================= scale loader (1-D x 1-D block scales; MX: warps 2 and 3) =================
             // Copies each contraction block's row and column scales into the ring with cp.async; the
             // slot's barrier hears from every lane when that lane's copies have landed, so neither this
             // warp nor the promotion warps ever hold a register waiting on a scale load from global
@@ -636,12 +636,15 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                 // Gathers the scale bytes of four contraction blocks at a time -- one aligned 16-byte load per
                 // operand row (a block's four 32-wide slices are one 32-bit word) -- and lays each block out
                 // as tcgen05.cp wants it: row r of a 128-row atom at byte 16 * (r % 32) + 4 * (r / 32), so a
-                // lane's four rows (lane, lane + 32, ...) are one 16-byte store.  The four-slot ring lets the
-                // loader run far enough ahead of the MMA issuer to hide the global round trip.
+                // lane's four rows (lane, lane + 32, ...) are one 16-byte store.  Warps 2 and 3 take the batches
+                // of four blocks in turn: while one waits for ring slots to store its batch, the other's loads
+                // for the next batch are already in flight, so the global round trip is never exposed (one
+                // loader warp left the tensor pipe idle for it once per four blocks: 37 % active).
                 Schedule sched(args, ctl);
                 Tile t;
-                uint32_t it = 0;
+                uint32_t it = 0, batch = 0;
                 bool ok     = true;
+                const uint32_t mine = warp & 1; // warp 2: even batches, warp 3: odd batches
                 // rows of 16 scale bytes can be read with one vector load when the pitch and base allow it
                 const bool vec = (args.a_sf_ld % 16 == 0) && (args.b_sf_ld % 16 == 0) &&
                                  ((reinterpret_cast<uintptr_t>(args.a_sf) | reinterpret_cast<uintptr_t>(args.b_sf)) & 15u) == 0;
@@ -660,6 +663,8 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     const bool vec_t     = vec && ((k_byte0 & 15) == 0);
                     uint4 w[12];
                     for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+                        if ((kb & 3) == 0) ++batch;
+                        if (((batch - 1) & 1) != mine) continue; // the other loader warp's batch
                         if ((kb & 3) == 0) {
 #pragma unroll
                             for (int i = 0; i < 12; ++i) {

@@ -44,12 +44,15 @@ template <int FMT, bool ZERO_IS_ONE> __device__ __forceinline__ int mx_byte(floa
     if (ZERO_IS_ONE && amax == 0.0f) return 127;
     return mx_biased_exponent<FMT>(amax);
 }
-// The clamp limit fmax * (byte << 23 read as fp32) -- byte 0 gives 0.0f, byte 255 gives +inf, as in the
-// reference -- and the exact reciprocal 2^(127 - byte) (subnormal for bytes 254 and 255).
-template <int FMT> __device__ __forceinline__ void mx_limits(int biased, float &lim, float &inv) {
-    lim = __fmul_rn(Fp8Max<FMT>::v, __uint_as_float((uint32_t) biased << 23));
+// The reference clamps a value to +-(fmax * scale), scale = (byte << 23) read as fp32, and divides by the
+// scale.  Here: multiply by the exact reciprocal 2^(127 - byte) (subnormal for bytes 254 and 255) and let the
+// saturating conversion clamp -- the same result for every finite value, because fmax * scale times the
+// reciprocal is exactly fmax.  Byte 0 is the one exception: its scale reads as 0.0f, the clamp limit is zero
+// and every value becomes +-0, which a multiplier of zero reproduces (sign included).
+__device__ __forceinline__ float mx_inverse(int biased) {
     const int e = 127 - biased; // 127 .. -128
-    inv         = (e >= -126) ? __uint_as_float((uint32_t) (e + 127) << 23) : __uint_as_float(1u << (149 + e));
+    if (biased == 0) return 0.0f;
+    return (e >= -126) ? __uint_as_float((uint32_t) (e + 127) << 23) : __uint_as_float(1u << (149 + e));
 }
 
 struct MxQuantArgs {
@@ -111,10 +114,10 @@ template <typename T> __device__ __forceinline__ void decode8(const uint4 &raw, 
     for (int i = 0; i < 8; ++i) v[i] = to_f32(e[i]);
 }
 
-template <int FMT> __device__ __forceinline__ uint32_t mx_cvt4(const float *v, float lim, float inv) {
+template <int FMT> __device__ __forceinline__ uint32_t mx_cvt4(const float *v, float inv) {
     float c[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(fminf(fmaxf(v[i], -lim), lim), inv);
+    for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(v[i], inv);
     return (uint32_t) cvt_fp8x2<FMT>(c[0], c[1]) | ((uint32_t) cvt_fp8x2<FMT>(c[2], c[3]) << 16);
 }
 
@@ -185,11 +188,10 @@ __global__ void __launch_bounds__(256, PTB_MXQ_MINB) mx_quant_kernel(const MxQua
             if (src0 + 4 * ps + rl >= src_end) continue; // only rows that exist are written
             const int64_t r  = out0 + 4 * ps + rl;
             const int biased = p.row_2d ? tile_b : mx_byte<FMT, GROUPED>(rmax[ps]);
-            float lim, inv;
-            mx_limits<FMT>(biased, lim, inv);
+            const float inv = mx_inverse(biased);
             float v[8];
             decode8<T>(raw[ps], v);
-            *reinterpret_cast<uint2 *>(q + r * p.N_pad + col) = make_uint2(mx_cvt4<FMT>(v, lim, inv), mx_cvt4<FMT>(v + 4, lim, inv));
+            *reinterpret_cast<uint2 *>(q + r * p.N_pad + col) = make_uint2(mx_cvt4<FMT>(v, inv), mx_cvt4<FMT>(v + 4, inv));
             if ((cl & 3) == 0) s[r * (p.N_pad / kMxBlock) + col / kMxBlock] = (uint8_t) biased;
         }
     }
@@ -202,12 +204,12 @@ __global__ void __launch_bounds__(256, PTB_MXQ_MINB) mx_quant_kernel(const MxQua
         // two passes of four columns each keep the live state small
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            float lim[4], inv[4];
+            float inv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int j      = 4 * h + i;
                 const int biased = p.col_2d ? tile_b : mx_byte<FMT, GROUPED>(cmax[j]);
-                mx_limits<FMT>(biased, lim[i], inv[i]);
+                inv[i] = mx_inverse(biased);
                 if (rl == 0 && col + j < p.N) s[(col + j) * (p.M_pad / kMxBlock) + row0 / kMxBlock] = (uint8_t) biased;
             }
             // w[ps]: this lane's row (4 ps + rl), columns 4 h .. 4 h + 3, one byte each
@@ -217,7 +219,7 @@ __global__ void __launch_bounds__(256, PTB_MXQ_MINB) mx_quant_kernel(const MxQua
                 const T *e = reinterpret_cast<const T *>(&raw[ps]) + 4 * h;
                 float c[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(fminf(fmaxf(to_f32(e[i]), -lim[i]), lim[i]), inv[i]);
+                for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(to_f32(e[i]), inv[i]);
                 w[ps] = (uint32_t) cvt_fp8x2<FMT>(c[0], c[1]) | ((uint32_t) cvt_fp8x2<FMT>(c[2], c[3]) << 16);
             }
             // 4x4 byte transpose across the lanes rl = 0..3 (lane bits 3 and 4): afterwards byte k of

@@ -41,6 +41,9 @@ def test_quantize_both_directions_match_oracle(dtype, fp8, shape, use_2d):
         x[1, :32] = 1e-30 if dtype == torch.bfloat16 else 6e-8
         x[2, :32] = 3e38 if dtype == torch.bfloat16 else 60000.0
         x[3, :32] = 2.0
+    if shape[0] > 4 and dtype == torch.bfloat16:
+        x[4, :32] = 0
+        x[4, 0], x[4, 1] = 1e-37, -1e-37  # a maximum below 2^-119: scale byte 0, every value becomes a signed zero
     recipe = ScalingRecipe(use_2d_block=use_2d)
     q_row, s_row, q_col, s_col = quantize_fp8_with_trans(
         x.to(DEV), fp8, MX, block_size=32, scaling_recipe=recipe, scaling_recipe_for_trans=recipe
