@@ -810,7 +810,7 @@ def run_grouped(args):
                   tr("fwd", (b_fwd + b_dgrad) / 2)),
             _roof("ptb_quant_fp8_block2d", "quant_block_kernel<128x128> (weight quantise)", 0, b_wq,
                   kernel_ms.get("ptb_quant_fp8_block2d", []), peaks, fp8_peak, tr("wq", b_wq)),
-            _roof("ptb_quant_fp8_segment_row_col", "quant_block_kernel<row + padded column copy> (activation and grad-out)", 0,
+            _roof("ptb_quant_fp8_segment_row_col", "seg_quant_stream_kernel (row + padded column copy of activation and grad-out)", 0,
                   (b_seg(K) + b_seg(N)) / 2, kernel_ms.get("ptb_quant_fp8_segment_row_col", []), peaks, fp8_peak),
         ]
         copy_key = "ptb_copy_segments_signal" if "ptb_copy_segments_signal" in kernel_ms else "ptb_copy_segments"
