@@ -50,6 +50,47 @@ def test_dispatch_and_combine_of_all_ranks_on_one_device(world, E, width):
     assert _lib.copy_segments_status() == 0
 
 
+@pytest.mark.parametrize("world,E,width", [(2, 6, 64), (8, 64, 512)])
+def test_signalled_copies_of_all_ranks_on_one_device(world, E, width):
+    """The arrival-flag form, every rank emulated on one GPU.  All copies are enqueued before any wait, on
+    one stream, so no wait kernel ever runs beside a kernel it depends on: each finds its flags set.
+    Checks the slot arithmetic (rank r's copy sets slot r of every destination's row), that an exchange
+    with nothing to send still signals, that the CTA counters are left at zero, and two rounds of
+    growing sequence numbers."""
+    g = torch.Generator().manual_seed(world + 100)
+    counts = torch.randint(0, 30, (world, E), generator=g)
+    counts[world - 1] = 0  # the last rank sends nothing and must signal all the same
+    xs = [torch.randn(int(counts[r].sum()), width, generator=g).to(torch.bfloat16).to(DEV) for r in range(world)]
+    tabs = [segment_tables(counts, r) for r in range(world)]
+    recv = [torch.zeros((max(t.rows_out, 1), width), dtype=torch.bfloat16, device=DEV) for t in tabs]
+    flags = [torch.zeros(world, dtype=torch.int32, device=DEV) for _ in range(world)]  # flags[d][s]: source s -> destination d
+    done = [torch.zeros(1, dtype=torch.int32, device=DEV) for _ in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    dst = (ctypes.c_void_p * world)(*[d.data_ptr() for d in recv])
+    for seq in (1, 2):
+        for r in range(world):
+            segs = tabs[r].dispatch.to(DEV)
+            slots = (ctypes.c_void_p * world)(*[flags[d].data_ptr() + 4 * r for d in range(world)])
+            n = segs.shape[0] if xs[r].shape[0] else 0
+            _lib.call("ptb_copy_segments_signal", xs[r].data_ptr() if n else None, dst, world, segs.data_ptr() if n else None, n,
+                      width * 2, (0, 5)[r % 2], slots, done[r].data_ptr(), seq, stream)
+        for d in range(world):
+            _lib.call("ptb_wait_flags", flags[d].data_ptr(), world, seq, stream)
+        torch.cuda.synchronize()
+        assert _lib.copy_segments_status() == 0
+        for d in range(world):
+            assert flags[d].tolist() == [seq] * world and int(done[d]) == 0
+    e_loc = E // world
+    for r in range(world):
+        want = torch.cat([xs[s][int(counts[s, :e].sum()) : int(counts[s, : e + 1].sum())]
+                          for e in range(r * e_loc, (r + 1) * e_loc) for s in range(world)])
+        assert torch.equal(recv[r][: want.shape[0]].view(torch.int16), want.view(torch.int16))
+    # a wait for a number that has already been passed returns at once as well
+    _lib.call("ptb_wait_flags", flags[0].data_ptr(), world, 1, stream)
+    torch.cuda.synchronize()
+    assert _lib.copy_segments_status() == 0
+
+
 def test_copy_segments_argument_checks_and_bad_rank_flag():
     src = torch.zeros(4, 16, dtype=torch.uint8, device=DEV)
     dst = torch.zeros(4, 16, dtype=torch.uint8, device=DEV)
