@@ -62,7 +62,7 @@ DENSE = {
                workload="llama3_8b_mlp_up_tensorwise_fp8_gemm_fwd"),
     "c3": dict(M=16384, N=8192, K=8192, gran="rowwise", bwd=True, w_scale=0.02,
                workload="llama3_70b_attn_out_rowwise_fp8_gemm_fwd_dgrad_wgrad"),
-    # not a BASELINE.json configuration: the c3 shape in the MXFP8 format (1x32 blocks, E8M0 scales)
+    # an extra configuration: the c3 shape in the MXFP8 format (1x32 blocks, E8M0 scales)
     "mx": dict(M=16384, N=8192, K=8192, gran="mx", bwd=True, w_scale=0.02,
                workload="llama3_70b_attn_out_mxfp8_gemm_fwd_dgrad_wgrad"),
 }
