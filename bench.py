@@ -794,7 +794,7 @@ def run_grouped(args):
         gemm_flops = 2 * rows0 * N * K
         # ncu dram__bytes_read + dram__bytes_write per launch on the captured 32-expert / 8192-row case of c4,
         # over the algorithmic bytes of that case: scaled to this launch by its algorithmic bytes
-        traffic_ratio = {"wgrad": 1.945e9 / 1.997e9, "fwd": 1.230e9 / 1.062e9, "wq": 2.790e9 / 2.819e9} \
+        traffic_ratio = {"wgrad": 1.941e9 / 1.997e9, "fwd": 1.227e9 / 1.062e9, "wq": 2.789e9 / 2.819e9} \
             if args.config == "c4" else {}
         b_wgrad = e_loc * N * K * 2 + pad0 * (N + K) * (1 + 4.0 / 128)
         b_fwd = e_loc * N * K + rows0 * (K + 2 * N)
@@ -803,7 +803,7 @@ def run_grouped(args):
         b_seg = lambda width: rows0 * width * (2 + 1 + 4.0 / 128) + pad0 * width * (1 + 4.0 / 128)  # noqa: E731
         tr = lambda k, b: (traffic_ratio[k] * b if k in traffic_ratio else None)  # noqa: E731
         roofs = [
-            _roof("ptb_grouped_gemm_fp8_variable_k", "fp8_gemm_kernel<block 1Dx1D, bf16> (grouped wgrad launch)", gemm_flops,
+            _roof("ptb_grouped_gemm_fp8_variable_k", "wgrad_pair_kernel<bf16> (grouped wgrad launch, 1-D x 1-D block scales)", gemm_flops,
                   b_wgrad, kernel_ms.get("ptb_grouped_gemm_fp8_variable_k", []), peaks, fp8_peak, tr("wgrad", b_wgrad)),
             _roof("ptb_grouped_gemm_fp8", "fp8_gemm_kernel<block 1x128 x 128x128, bf16> (grouped forward and dgrad launches)",
                   gemm_flops, (b_fwd + b_dgrad) / 2, kernel_ms.get("ptb_grouped_gemm_fp8", []), peaks, fp8_peak,
