@@ -259,6 +259,7 @@ struct __align__(16) SharedCtl {
     uint64_t tmem_full[kMaxAccBufs];
     uint64_t tmem_empty[kMaxAccBufs];
     uint32_t tmem_base;
+    uint32_t sf_batches_done; // MX scale loaders: batches of four blocks whose slots have been claimed and filled
     int total_tiles;
     int sched_q, sched_rem; // grid stride = sched_q * tiles_n + sched_rem
     int tile_prefix[kMaxGroups + 1];
@@ -431,6 +432,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
         if (args.use_tma_store) tma_prefetch_map(&args.tm_c);
     }
     if (threadIdx.x == 32) {
+        ctl->sf_batches_done = 0;
         ctl->sched_q   = (int) gridDim.x / args.tiles_n;
         ctl->sched_rem = (int) gridDim.x % args.tiles_n;
     }
@@ -662,23 +664,52 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                     const int k_byte0    = t.k_row0 / 32;
                     const bool vec_t     = vec && ((k_byte0 & 15) == 0);
                     uint4 w[12];
-                    for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-                        if ((kb & 3) == 0) ++batch;
-                        if (((batch - 1) & 1) != mine) continue; // the other loader warp's batch
-                        if ((kb & 3) == 0) {
+                    int loaded_kb = -1; // first block of the batch whose words are in w
+                    auto load_batch = [&](int kb0) {
 #pragma unroll
-                            for (int i = 0; i < 12; ++i) {
-                                const uint8_t *src = (i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld
-                                                            : args.b_sf + (b_row0 + row[i]) * args.b_sf_ld) + k_byte0 + 4 * kb;
-                                if (vec_t && kb + 4 <= t.num_kb) {
-                                    w[i] = __ldg(reinterpret_cast<const uint4 *>(src));
-                                } else {
-                                    const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
-                                    w[i].x = __ldg(s32);
-                                    w[i].y = kb + 1 < t.num_kb ? __ldg(s32 + 1) : 0u;
-                                    w[i].z = kb + 2 < t.num_kb ? __ldg(s32 + 2) : 0u;
-                                    w[i].w = kb + 3 < t.num_kb ? __ldg(s32 + 3) : 0u;
+                        for (int i = 0; i < 12; ++i) {
+                            const uint8_t *src = (i < 4 ? args.a_sf + (int64_t) row[i] * args.a_sf_ld
+                                                        : args.b_sf + (b_row0 + row[i]) * args.b_sf_ld) + k_byte0 + 4 * kb0;
+                            if (vec_t && kb0 + 4 <= t.num_kb) {
+                                w[i] = __ldg(reinterpret_cast<const uint4 *>(src));
+                            } else {
+                                const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
+                                w[i].x = __ldg(s32);
+                                w[i].y = kb0 + 1 < t.num_kb ? __ldg(s32 + 1) : 0u;
+                                w[i].z = kb0 + 2 < t.num_kb ? __ldg(s32 + 2) : 0u;
+                                w[i].w = kb0 + 3 < t.num_kb ? __ldg(s32 + 3) : 0u;
+                            }
+                        }
+                        loaded_kb = kb0;
+                    };
+                    for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+                        const bool start = (kb & 3) == 0;
+                        if (start) ++batch;
+                        const bool own = ((batch - 1) & 1) == mine;
+                        if (start) {
+                            // own batch: fetch it unless it is already here; the other warp's batch: fetch the one
+                            // after it (batches alternate, so that one is this warp's) before waiting on the ring
+                            if (own) {
+                                if (loaded_kb != kb) load_batch(kb);
+                            } else if (kb + 4 < t.num_kb) {
+                                load_batch(kb + 4);
+                            }
+                        }
+                        if (!own) continue;
+                        // Hand-over between the two warps: a batch's slots are claimed only after the previous
+                        // batch's owner has passed all of its waits.  A parity wait tells "this phase is over"
+                        // from "the previous phase is over" only for a waiter within one phase of the barrier;
+                        // the owner of batch b last waited on these slots for batch b - 2, and without the
+                        // hand-over it could find a slot's barrier still one phase back, pass at once and
+                        // overwrite a block the tensor cores have not read.
+                        if (start) {
+                            const volatile uint32_t *done = &ctl->sf_batches_done;
+                            if (*done != batch - 1) {
+                                const uint64_t t0 = globaltimer_ns();
+                                while (*done != batch - 1) {
+                                    if (globaltimer_ns() - t0 > kWaitLimitNs) { ok = false; break; }
                                 }
+                                if (!ok) break;
                             }
                         }
                         const int slot = it % kScaleSlots;
@@ -692,9 +723,20 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
 #undef PTB_SFW
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // tcgen05.cp reads through the async proxy
                         mbar_arrive(smem_u32(&ctl->sc_full[slot]));
+                        if ((kb & 3) == 3 || kb == t.num_kb - 1) {
+                            // last block of this warp's batch: the other warp may claim the slots that follow
+                            __syncwarp();
+                            if (lane == 0) *reinterpret_cast<volatile uint32_t *>(&ctl->sf_batches_done) = batch;
+                        }
                     }
                 }
-                if (!ok && lane == 0) atomicExch(&g_gemm_status, 4);
+                if (!ok) {
+                    // release a partner that may be waiting for the hand-over; it will run into its own limits
+                    if (lane == 0) {
+                        *reinterpret_cast<volatile uint32_t *>(&ctl->sf_batches_done) = 0xffffffffu;
+                        atomicExch(&g_gemm_status, 4);
+                    }
+                }
             }
         }
     } else {

@@ -227,3 +227,54 @@ def test_grouped_gemm_forward_backward_vs_oracle(fmt, lens, NK):
             assert bd.grad[g].abs().max().item() == 0.0
     hp = torch.cat([a[go[g] : go[g + 1]].float() @ b[g].float().t() for g in range(G)])
     assert O.snr_db(hp, out.float().cpu()) > 25
+
+
+# ---- long contraction extents and many tiles per CTA: the scale ring goes round many times ------------------
+from primus_turbo_b200 import _lib  # noqa: E402
+from primus_turbo_b200.pytorch.kernels.gemm_impl import (  # noqa: E402
+    gemm_mxfp8_impl,
+    grouped_gemm_mxfp8_impl,
+    grouped_gemm_mxfp8_variable_k_impl,
+)
+
+
+@pytest.mark.parametrize("mnk", [(512, 768, 8192), (4096, 4096, 2048), (300, 264, 7168 + 128)])
+def test_gemm_long_k_and_many_tiles(mnk):
+    M, N, K = mnk
+    a = _mk((M, K), torch.bfloat16, seed=11)
+    b = _mk((N, K), torch.bfloat16, seed=12, scale=0.05)
+    aq, a_s = O.quant_mxfp8(a, torch.float8_e4m3fn, 1)
+    bq, b_s = O.quant_mxfp8(b, torch.float8_e4m3fn, 1, True)
+    _lib.gemm_status(reset=True)
+    out = gemm_mxfp8_impl(aq.to(DEV), a_s.to(DEV), bq.to(DEV), b_s.to(DEV), torch.bfloat16)
+    torch.cuda.synchronize()
+    assert _lib.gemm_status() == 0, "a bounded wait inside the kernel ran out"
+    ref = O.gemm_mxfp8_nt(aq, a_s, bq, b_s)
+    assert O.rel_frobenius(ref, out.cpu()) <= 1e-2
+
+
+def test_grouped_gemm_many_groups_long_k():
+    g = torch.Generator().manual_seed(21)
+    G, N, K = 96, 512, 7168
+    lens = torch.randint(0, 90, (G,), generator=g)
+    lens[5] = 0
+    lens[17] = 300
+    M = int(lens.sum())
+    a = _mk((M, K), torch.bfloat16, seed=1)
+    b = _mk((G, N, K), torch.bfloat16, seed=2, scale=0.05)
+    gy = _mk((M, N), torch.bfloat16, seed=3, scale=0.01)
+    go = torch.cat([lens.new_zeros(1), lens.cumsum(0)]).tolist()
+    E4 = torch.float8_e4m3fn
+    a_row, a_rs, a_col, a_cs, _, c_offs, _ = O.quant_mxfp8_grouped(a, E4, go, 1)
+    g_row, g_rs, g_col, g_cs, _, _, _ = O.quant_mxfp8_grouped(gy, E4, go, 1)
+    b_rows = [O.quant_mxfp8(b[i], E4, 1, True) for i in range(G)]
+    bq, bs = torch.stack([p[0] for p in b_rows]), torch.stack([p[1] for p in b_rows])
+    offs_dev = torch.tensor(go, dtype=torch.int64, device=DEV)
+    _lib.gemm_status(reset=True)
+    out = grouped_gemm_mxfp8_impl(a_row.to(DEV), a_rs.to(DEV), bq.to(DEV), bs.to(DEV), offs_dev, torch.bfloat16)
+    gw = grouped_gemm_mxfp8_variable_k_impl(g_col.to(DEV), g_cs.to(DEV), a_col.to(DEV), a_cs.to(DEV),
+                                            torch.tensor(c_offs, dtype=torch.int64, device=DEV), torch.bfloat16)
+    torch.cuda.synchronize()
+    assert _lib.gemm_status() == 0, "a bounded wait inside the kernel ran out"
+    assert O.rel_frobenius(O.grouped_gemm_mxfp8(a_row, a_rs, bq, bs, go), out.cpu()) <= 1e-2
+    assert O.rel_frobenius(O.grouped_gemm_mxfp8_variable_k(g_col, g_cs, a_col, a_cs, c_offs), gw.cpu()) <= 1e-2
