@@ -638,7 +638,14 @@ def run_grouped(args):
             board = EP.SharedCountsBoard(E, group=host_group)  # ranks of one machine: counts through shared memory
         except Exception as exc:  # noqa: BLE001 - keep the gloo group
             print(f"[bench] shared counts board unavailable ({exc!r}); using gloo", file=sys.stderr)
-    qcfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
+    if args.granularity == "mx":
+        from primus_turbo_b200.pytorch.core.low_precision import ScaleDtype
+
+        qcfg = Float8QuantConfig(granularity=ScalingGranularity.MX_BLOCKWISE, block_size=32, scale_dtype=ScaleDtype.E8M0)
+        args.no_cached = True  # pre-quantised weights are a BLOCKWISE feature
+        args.no_cpu_baseline = True  # the CPU arm times the benchmark's own (128-block) format
+    else:
+        qcfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
     e_loc = E // world
 
     # ---- routing: global counts, expert placement, this rank's rows ---------------------------------------
@@ -829,14 +836,15 @@ def run_grouped(args):
         wl = _workload_config(args.config)
         wl.update({"experts": E, "routed_rows": ROWS, "experts_per_gpu": e_loc, "parallelism": f"ep{world}",
                    "exchange": (args.exchange if world > 1 else None), "placement": (args.placement if world > 1 else None),
-                   "ep_overlap": (bool(args.ep_overlap) if world > 1 else None),
+                   "ep_overlap": (bool(args.ep_overlap) if world > 1 else None), "granularity": args.granularity,
                    "ep_ordering": (args.ep_ordering if world > 1 and args.exchange == "peer" else None),
                    "load_imbalance_max_over_mean_rows": imbalance,
                    "load_imbalance_contiguous_placement": imbalance_contiguous,
                    "tile_padding_rows_over_rows": pad0 / max(rows0, 1),
                    "l2": f"inputs larger than L2 ({e_loc * N * K / 1e9:.2f} GB of FP8 weights per pass)"})
         line = {
-            "metric": METRIC[args.config], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": (METRIC[args.config] if args.granularity == "blockwise" else METRIC[args.config].replace("blockwise_fp8", "mxfp8")),
+            "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 operands, fp32 accumulate, bf16 in/out", "data": "synthetic",
             "config": wl, "per_gpu_tflops": value / world, "pct_of_fp8_peak_per_gpu": 100.0 * value / world / fp8_peak,
@@ -890,6 +898,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--no-cached", action="store_true", help="skip the pass with weights quantised ahead of time")
+    ap.add_argument("--granularity", choices=["blockwise", "mx"], default="blockwise",
+                    help="grouped configurations: 128-block scales (the benchmark's) or MXFP8 (1x32 blocks, E8M0 scales)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: rows written into the owners' IPC-mapped buffers by this library's copy kernel, or "
                          "NCCL all-to-alls plus a permutation pass")

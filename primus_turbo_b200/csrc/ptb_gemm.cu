@@ -707,6 +707,7 @@ __global__ void __launch_bounds__(Geo<BN, DEEP>::kThreads, 1) fp8_gemm_kernel(co
                             if (*done != batch - 1) {
                                 const uint64_t t0 = globaltimer_ns();
                                 while (*done != batch - 1) {
+                                    __nanosleep(40);
                                     if (globaltimer_ns() - t0 > kWaitLimitNs) { ok = false; break; }
                                 }
                                 if (!ok) break;
