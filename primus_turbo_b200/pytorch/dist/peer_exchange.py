@@ -227,7 +227,7 @@ class PeerExchange:
 
             k, seq = self._last
             with torch.cuda.device(self.device):
-                _lib.call("ptb_wait_flags", self._flag_ptrs[self.rank] + 4 * k * self.world, self.world, seq,
+                _lib.call("ptb_wait_flags", self._flag_ptrs[self.rank] + 4 * k * self.world, self.world, seq & 0xFFFFFFFF,
                           torch.cuda.current_stream(self.device).cuda_stream)
             return
         if self.device.type == "cuda":
