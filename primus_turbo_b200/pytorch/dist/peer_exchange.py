@@ -87,13 +87,12 @@ def _device_copy(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row
                   num_ctas, torch.cuda.current_stream(src.device).cuda_stream)
 
 
-def _device_copy_signal(src: torch.Tensor, dst_ptrs: List[int], segs: torch.Tensor, row_bytes: int, num_ctas: int,
-                        flag_slots: List[int], done_counter: int, seq: int) -> None:
+def _device_copy_signal(src: torch.Tensor, arr, segs: torch.Tensor, row_bytes: int, num_ctas: int, slots, done_counter: int,
+                        seq: int) -> None:
+    """``arr`` / ``slots``: ctypes arrays of the destinations' region bases and of this rank's flag slot in each."""
     from primus_turbo_b200 import _lib
 
-    n = len(dst_ptrs)
-    arr = (ctypes.c_void_p * n)(*dst_ptrs)
-    slots = (ctypes.c_void_p * n)(*flag_slots)
+    n = len(arr)
     nseg = segs.shape[0] if src.shape[0] else 0
     with torch.cuda.device(src.device):
         _lib.call("ptb_copy_segments_signal", src.data_ptr() if nseg else None, arr, n, segs.data_ptr() if nseg else None,
@@ -168,6 +167,7 @@ class PeerExchange:
         self._key_index: Dict[Tuple[str, int, str], int] = {}
         self._seq: Dict[int, int] = {}
         self._last: Optional[Tuple[int, int]] = None  # (key index, sequence number) of the latest push
+        self._signal_args: Dict[int, Tuple] = {}
         if ordering == "flags":
             # [MAX_KEYS, world] arrival slots (row k: one slot per source rank) and one CTA counter per key,
             # zeroed; the slots are published to the other ranks like a region
@@ -251,6 +251,7 @@ class PeerExchange:
             self._regions[key] = (local, [], [])
         if self.ordering == "flags":
             self._flag_views, self._flag_ptrs = [self._flags], []
+            self._signal_args.clear()
         gc.collect()
         if self.device.type == "cuda":
             torch.cuda.ipc_collect()
@@ -279,9 +280,14 @@ class PeerExchange:
             seq = self._seq.get(k, 0) + 1
             self._seq[k] = seq
             self._last = (k, seq)
-            _device_copy_signal(src, ptrs, segs, row_bytes, self.num_ctas,
-                                [p + 4 * (k * self.world + self.rank) for p in self._flag_ptrs],
-                                self._flag_ptrs[self.rank] + 4 * (self.MAX_KEYS * self.world + k), seq & 0xFFFFFFFF)
+            cached = self._signal_args.get(k)
+            if cached is None:  # the pointer arrays of a region never change: build them once
+                n = len(ptrs)
+                cached = ((ctypes.c_void_p * n)(*ptrs),
+                          (ctypes.c_void_p * n)(*[p + 4 * (k * self.world + self.rank) for p in self._flag_ptrs]),
+                          self._flag_ptrs[self.rank] + 4 * (self.MAX_KEYS * self.world + k))
+                self._signal_args[k] = cached
+            _device_copy_signal(src, cached[0], segs, row_bytes, self.num_ctas, cached[1], cached[2], seq & 0xFFFFFFFF)
         elif segs.shape[0] and src.shape[0]:
             self._copy(src, ptrs, segs, row_bytes, self.num_ctas)
         # `.data`: a tensor over the same bytes with its own version counter -- the region is rewritten by

@@ -180,3 +180,31 @@ def _(a, b, a_scales, b_scales, group_lens, group_offs, trans_a, trans_b, trans_
     G = group_offs.shape[0] - 1
     m, n = (b.shape[1], a.shape[1]) if trans_c else (a.shape[1], b.shape[1])
     return torch.empty((G, m, n), dtype=out_dtype, device=a.device)
+
+
+# ---- eager fast path ----------------------------------------------------------------------------------------
+# Outside tracing, a registered op's Python dispatcher (autograd wrapper, redispatch, dynamo frame guard) costs
+# about 70 us per call -- several times the ctypes call it wraps, and with six such calls per grouped-GEMM
+# step it is most of the host time of a step, which is what paces a short multi-GPU step.  The public names of
+# this module therefore run the op's own body directly in plain eager mode and go through the registered op
+# only while compiling or under a dispatch mode (FakeTensorMode, functionalisation, ...), where the op and its
+# fake kernel are what the tracer needs.  Same function either way; `.op` is the registered op.
+def _with_eager_fast_path(op):
+    body = op._init_fn  # the undecorated function the op was created from
+
+    def call(*args, **kwargs):
+        if torch.compiler.is_compiling() or torch._C._len_torch_dispatch_stack() > 0:
+            return op(*args, **kwargs)
+        return body(*args, **kwargs)
+
+    call.__name__ = call.__qualname__ = body.__name__
+    call.__doc__ = body.__doc__
+    call.op = op
+    return call
+
+
+for _name in ("quantize_fp8_tensorwise", "quantize_fp8_rowwise", "quant_fp8_blockwise", "quant_fp8_blockwise_dual",
+              "quant_fp8_blockwise_for_weight", "quant_fp8_blockwise_segment_m_row_col", "dequantize_fp8", "gemm_fp8_impl",
+              "grouped_gemm_fp8_impl", "grouped_gemm_fp8_variable_k_impl"):
+    globals()[_name] = _with_eager_fast_path(globals()[_name])
+del _name
