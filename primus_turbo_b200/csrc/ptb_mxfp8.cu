@@ -347,14 +347,16 @@ int ptb_quant_mxfp8_grouped(const void *x, int x_dtype, int64_t M, int64_t N, co
     PTB_REQUIRE(G >= 1 && M >= 0 && N >= 0, PTB_ERR_ARG, "grouped MXFP8 quantise: at least one group, non-negative extents");
     PTB_REQUIRE(N % kMxBlock == 0, PTB_ERR_ARG, "N (%lld) must be divisible by 32", (long long) N);
     PTB_REQUIRE(row_align == 1 || row_align == 32, PTB_ERR_ARG, "row_align must be 1 or 32");
-    PTB_REQUIRE(group_offs && q_row && s_row && q_col && s_col && row_lens_padded && row_offs_padded && col_lens_padded &&
-                    col_offs_padded && block_table,
+    // with no row at all (an expert-parallel rank that received nothing) x and an unpadded row copy are empty
+    PTB_REQUIRE(group_offs && (M == 0 || (q_row && s_row)) && q_col && s_col && row_lens_padded && row_offs_padded &&
+                    col_lens_padded && col_offs_padded && block_table,
                 PTB_ERR_ARG, "grouped MXFP8 quantise: null pointer");
     PTB_REQUIRE(M < (1ll << 31), PTB_ERR_TOO_LARGE, "grouped MXFP8 quantise: too many rows");
     PTB_REQUIRE((N == 0 || aligned16(x)) && aligned16(q_row) && aligned16(q_col) && aligned16(block_table), PTB_ERR_ARG,
                 "MXFP8 quantise needs 16-byte aligned input, FP8 outputs and block table");
     MxQuantArgs a;
-    a.x = x; a.q_row = (uint8_t *) q_row; a.s_row = (uint8_t *) s_row; a.q_col = (uint8_t *) q_col; a.s_col = (uint8_t *) s_col;
+    a.x = x ? x : q_col; // never dereferenced without rows; the zero-size copies still get a mapped address
+    a.q_row = (uint8_t *) q_row; a.s_row = (uint8_t *) s_row; a.q_col = (uint8_t *) q_col; a.s_col = (uint8_t *) s_col;
     a.M = M; a.N = N;
     a.M_pad = cdiv<int64_t>(M + G * kMxPad, kMxPad) * kMxPad; // rows the column layout is allocated for (upper bound)
     a.N_pad = cdiv<int64_t>(N, kMxPad) * kMxPad;

@@ -1151,8 +1151,10 @@ int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t
     PTB_REQUIRE(M >= 0 && N >= 0 && G >= 0, PTB_ERR_ARG, "quant_segment_row_col: negative size");
     PTB_REQUIRE(group_offs && var_k_lens && var_k_offs, PTB_ERR_ARG, "quant_segment_row_col: null group arrays");
     PTB_REQUIRE(N > 0, PTB_ERR_ARG, "quant_segment_row_col: N must be positive");
-    PTB_REQUIRE(x && q_row && q_col_padded && s_row && s_col_padded, PTB_ERR_ARG,
-                "quant_segment_row_col: null pointer");
+    // a rank of an expert-parallel job may receive no row at all: the tensors with M rows are then empty
+    // (null), the padded layout is still written (all groups empty) and nothing else happens
+    PTB_REQUIRE(M == 0 || (x && q_row && s_row), PTB_ERR_ARG, "quant_segment_row_col: null pointer");
+    PTB_REQUIRE(M + G == 0 || (q_col_padded && s_col_padded), PTB_ERR_ARG, "quant_segment_row_col: null pointer");
     BlockQuantArgs a{};
     a.x = x; a.B = 1; a.M = M; a.N = N; a.G = G;
     a.q_row = (uint8_t *) q_row; a.s_row = s_row;
@@ -1193,8 +1195,8 @@ int ptb_swiglu_quant_fp8_segment_row_col(const void *x, int x_dtype, const float
     PTB_REQUIRE(N % 8 == 0, PTB_ERR_ALIGN, "swiglu_quant_segment_row_col: the hidden size must be a multiple of 8");
     PTB_REQUIRE(x_dtype == PTB_BF16 || x_dtype == PTB_F16, PTB_ERR_ARG, "swiglu_quant_segment_row_col: x must be bf16 or fp16");
     PTB_REQUIRE(group_offs && var_k_lens && var_k_offs, PTB_ERR_ARG, "swiglu_quant_segment_row_col: null group arrays");
-    PTB_REQUIRE(x && probs && q_row && q_col_padded && s_row && s_col_padded, PTB_ERR_ARG,
-                "swiglu_quant_segment_row_col: null pointer");
+    PTB_REQUIRE(M == 0 || (x && probs && q_row && s_row), PTB_ERR_ARG, "swiglu_quant_segment_row_col: null pointer");
+    PTB_REQUIRE(M + G == 0 || (q_col_padded && s_col_padded), PTB_ERR_ARG, "swiglu_quant_segment_row_col: null pointer");
     PTB_REQUIRE(aligned16(x), PTB_ERR_ALIGN, "swiglu_quant_segment_row_col: x must be 16-byte aligned");
     PTB_REQUIRE(block_table == nullptr || M < 2147483647LL, PTB_ERR_TOO_LARGE,
                 "swiglu_quant_segment_row_col: the block table holds 32-bit row numbers");

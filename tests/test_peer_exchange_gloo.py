@@ -20,7 +20,7 @@ import torch.multiprocessing as mp
 from primus_turbo_b200.pytorch.dist.peer_exchange import segment_tables
 
 H = 8
-SHAPES = [(2, 6), (4, 8)]
+SHAPES = [(2, 6), (4, 8), (8, 16)]
 
 
 def _routing(seed, WORLD, E, step=0):
@@ -42,7 +42,7 @@ def _copy_loop(src, dst_tensors, segs):
             dst_tensors[r][d : d + n] = src[s : s + n]
 
 
-@pytest.mark.parametrize("WORLD,E", SHAPES + [(8, 16)])
+@pytest.mark.parametrize("WORLD,E", SHAPES)
 def test_segment_tables_place_every_row(WORLD, E):
     counts, xs = _routing(3, WORLD, E)
     e_loc = E // WORLD
