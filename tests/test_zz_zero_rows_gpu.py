@@ -13,7 +13,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from primus_turbo_b200 import _lib  # noqa: E402
-from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity  # noqa: E402
+from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScaleDtype, ScalingGranularity  # noqa: E402
 
 DEV = "cuda"
 E4 = torch.float8_e4m3fn
@@ -56,8 +56,10 @@ def test_grouped_gemm_without_rows_gives_a_zero_weight_gradient(granularity, G):
     from primus_turbo_b200.pytorch.ops import grouped_gemm_fp8
 
     K, N = 512, 384
-    block = 128 if granularity == ScalingGranularity.BLOCKWISE else 32
-    cfg = Float8QuantConfig(granularity=granularity, block_size=block)
+    if granularity == ScalingGranularity.BLOCKWISE:
+        cfg = Float8QuantConfig(granularity=granularity, block_size=128)
+    else:
+        cfg = Float8QuantConfig(granularity=granularity, block_size=32, scale_dtype=ScaleDtype.E8M0)
     lens, _ = _groups(G)
     a = torch.empty((0, K), dtype=torch.bfloat16, device=DEV, requires_grad=True)
     w = (torch.randn(G, N, K, device=DEV) * 0.02).to(torch.bfloat16).requires_grad_(True)
