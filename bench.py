@@ -632,6 +632,10 @@ def run_grouped(args):
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
+        # The job's collectives are all-to-alls, barriers and scalar reductions: in-switch reduction buys nothing
+        # here, and a rank that dies while its memory is bound to an NVLink multicast object raises faults on
+        # the other ranks' GPUs.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
         host_group = dist.new_group(backend="gloo")  # CPU group: set-up traffic and the fallback count gather
         try:

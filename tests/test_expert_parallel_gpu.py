@@ -32,6 +32,8 @@ def _data(WORLD):
 
 def _worker(rank, store_path, q, overlap, WORLD):
     torch.cuda.set_device(rank)
+    # a rank that fails leaves while the others still hold the communicator: keep NVLink multicast objects out of it
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     store = dist.FileStore(store_path, WORLD)
     dist.init_process_group("nccl", store=store, rank=rank, world_size=WORLD, device_id=torch.device("cuda", rank))
     try:
@@ -92,13 +94,20 @@ def test_expert_parallel_matches_single_gpu(overlap, WORLD):
         for p in procs:
             p.start()
         res = {}
-        for _ in range(WORLD):
-            r, out, gx, gw = q.get(timeout=300)
-            assert gx is not None, f"rank {r} failed: {out}"
-            res[r] = (torch.tensor(out), torch.tensor(gx), torch.tensor(gw))
-        for p in procs:
-            p.join(timeout=120)
-            assert p.exitcode == 0
+        try:
+            for _ in range(WORLD):
+                r, out, gx, gw = q.get(timeout=300)
+                assert gx is not None, f"rank {r} failed: {out}"
+                res[r] = (torch.tensor(out), torch.tensor(gx), torch.tensor(gw))
+            for p in procs:
+                p.join(timeout=120)
+                assert p.exitcode == 0
+        finally:
+            # after a failure the surviving ranks wait for the one that left: end exactly the children started here
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+                    p.join(timeout=30)
 
     from oracle import fp8_oracle as O
     from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, ScalingGranularity

@@ -28,6 +28,7 @@ def _worker(rank, store_path, q, backend, quant):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     if backend == "nccl":
         torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # a failing rank must not leave NVLink multicast objects behind
     dist.init_process_group(backend, store=dist.FileStore(store_path, WORLD), rank=rank, world_size=WORLD)
     try:
         from primus_turbo_b200.pytorch.core.low_precision import Float8QuantConfig, Format
@@ -59,13 +60,19 @@ def _run(backend, quant):
         for p in procs:
             p.start()
         res = {}
-        for _ in range(WORLD):
-            r, y, gx, go = q.get(timeout=180)
-            assert gx is not None, f"rank {r} failed: {y}"
-            res[r] = (torch.tensor(y), torch.tensor(gx), torch.tensor(go))
-        for p in procs:
-            p.join(timeout=60)
-            assert p.exitcode == 0
+        try:
+            for _ in range(WORLD):
+                r, y, gx, go = q.get(timeout=180)
+                assert gx is not None, f"rank {r} failed: {y}"
+                res[r] = (torch.tensor(y), torch.tensor(gx), torch.tensor(go))
+            for p in procs:
+                p.join(timeout=60)
+                assert p.exitcode == 0
+        finally:
+            for p in procs:  # after a failure: end exactly the children started here
+                if p.is_alive():
+                    p.terminate()
+                    p.join(timeout=30)
     return res
 
 
