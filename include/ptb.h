@@ -126,6 +126,8 @@ int ptb_quant_fp8_block2d(const void *w, int w_dtype, int64_t B, int64_t M, int6
  * block_table: optional workspace of ceil((M + 128*G) / 128) * 8 bytes (8-byte aligned), written by the
  * call: with it every tile finds its source rows with one load; NULL makes every tile scan the G
  * offsets instead (same results).
+ * M == 0 (no row at all, e.g. an expert-parallel rank whose experts received nothing): x, q_row and s_row
+ * may be NULL; var_k_lens / var_k_offs and the block table are still written (every group empty).
  * Replaces torch op quantize_fp8_blockwise_segment_m_row_col (bindings_pytorch.cpp:35,
  * quantization.cpp:1382-1439). */
 int ptb_quant_fp8_segment_row_col(const void *x, int x_dtype, int64_t M, int64_t N, int64_t G,
@@ -152,6 +154,7 @@ int ptb_swiglu_probs_bwd(const void *grad_out, const void *x, int dtype, const f
  * activation: every tile computes act = round_to_dtype(swiglu(x)) in registers and quantises it, so the
  * six outputs equal ptb_swiglu_probs_fwd followed by ptb_quant_fp8_segment_row_col byte for byte while
  * moving 6 instead of 10 bytes per activation element.  N % 8 == 0; x bf16 / fp16, 16-byte aligned.
+ * M == 0: x, probs, q_row and s_row may be NULL, as for ptb_quant_fp8_segment_row_col.
  * Fuses the reference's swiglu_with_probs (primus_turbo/pytorch/ops/activation.py:23-83) with its
  * grouped activation quantise (quantization_impl.py:379-464); the reference runs them as two kernels. */
 int ptb_swiglu_quant_fp8_segment_row_col(const void *x, int x_dtype, const float *probs, int64_t M,
@@ -314,7 +317,8 @@ int ptb_quant_mxfp8(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N,
  * A block whose maximum is zero takes scale byte 127 (1.0), as the reference's grouped kernel does.
  * Also written: the padded lengths and offsets of both layouts (device int64 [G] / [G+1]).
  * block_table: workspace of 16 bytes per 128-row block of the column layout (M_col/128 blocks),
- * 16-byte aligned.  Replaces grouped_quantize_mxfp8_dual
+ * 16-byte aligned.  M == 0: x (and, with row_align 1, q_row / s_row) may be NULL; the layouts and the
+ * zero columns are still written.  Replaces grouped_quantize_mxfp8_dual
  * (csrc/pytorch/quantization/quantization.cpp:1075-1195; the reference's row layout is row_align = 32). */
 int ptb_quant_mxfp8_grouped(const void *x, int x_dtype, int64_t M, int64_t N, const int64_t *group_offs,
                             int64_t G, int64_t row_align, void *q_row, void *s_row, void *q_col,
