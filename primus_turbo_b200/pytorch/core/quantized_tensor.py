@@ -2,7 +2,10 @@
 
 API-compatible with primus_turbo/pytorch/core/quantized_tensor.py:113-145 (check_quantized_tensor),
 :148-835 (QuantizedTensor) and :884-894 (QuantizedTensorPair) for the FP8 tensorwise / rowwise /
-blockwise granularities.  MX and FP4 payloads are not part of this build.
+blockwise granularities and for (non-grouped) MXFP8 payloads: an MX tensor holds its FP8 bytes padded to a
+multiple of 128 along the quantised direction (axis -1: ``[.., M, K_pad]``; axis -2: the TRANSPOSED copy
+``[.., K, M_pad]``) and one E8M0 byte per 32 elements; its wrapper shape stays the logical one.  Grouped MX
+activations (the reference's per-group padded layouts) and FP4 payloads are not part of this build.
 """
 
 from __future__ import annotations
@@ -12,6 +15,8 @@ from typing import Any, NamedTuple, Optional, Tuple, Union
 import torch
 
 from primus_turbo_b200.pytorch.core.low_precision import (
+    MXFP8_BLOCK_SIZE,
+    MXFP8_PADDING_ALIGN_SIZE,
     Float8QuantConfig,
     ScalingGranularity,
     ScalingRecipe,
@@ -20,7 +25,19 @@ from primus_turbo_b200.pytorch.core.low_precision import (
 )
 
 _FP8 = (float8_e4m3, float8_e5m2)
-_GRANS = (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE, ScalingGranularity.BLOCKWISE)
+_GRANS = (
+    ScalingGranularity.TENSORWISE,
+    ScalingGranularity.ROWWISE,
+    ScalingGranularity.BLOCKWISE,
+    ScalingGranularity.MX_BLOCKWISE,
+)
+
+
+def _pad_inner_dim(shape, align: int):
+    """``shape`` with its last extent rounded up to a multiple of ``align`` (the MX payloads' inner padding)."""
+    if len(shape) == 0 or align <= 1:
+        return tuple(shape)
+    return (*shape[:-1], (shape[-1] + align - 1) // align * align)
 
 
 def _norm_axis(axis: Optional[int], ndim: int) -> Optional[int]:
@@ -115,6 +132,9 @@ class QuantizedTensor(torch.Tensor):
         assert granularity in _GRANS, f"Unsupported granularity {granularity}"
         if granularity == ScalingGranularity.BLOCKWISE:
             assert block_size is not None, "block_size must be provided for BLOCKWISE"
+        if granularity == ScalingGranularity.MX_BLOCKWISE:
+            assert block_size == MXFP8_BLOCK_SIZE, "block_size must be MXFP8_BLOCK_SIZE for MX_BLOCKWISE"
+            assert scaling_recipe is not None, "scaling_recipe must be provided for MX_BLOCKWISE"
         if granularity != ScalingGranularity.TENSORWISE:
             assert axis is not None, "axis must be provided for non-TENSORWISE granularity"
         grouped = group_lens is not None
@@ -123,7 +143,7 @@ class QuantizedTensor(torch.Tensor):
             # Tensorwise / rowwise scales do not depend on the grouping: the packed [sum(M_g), K]
             # tensor is quantised as a whole and only carries the group metadata along.
             assert granularity in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE), (
-                "grouped BLOCKWISE activations are quantised inside grouped_gemm_fp8"
+                "grouped BLOCKWISE / MX_BLOCKWISE activations are quantised inside grouped_gemm_fp8"
             )
             assert hp_tensor.ndim == 2 and group_lens.is_cuda
             g_lens, g_offs = group_lens, group_offs_from_lens(group_lens)
@@ -196,7 +216,7 @@ class QuantizedTensor(torch.Tensor):
         """Back to the original high-precision dtype: cast(float(q) * scale_inv)."""
         from primus_turbo_b200.pytorch.ops.quantization import dequantize_fp8
 
-        return dequantize_fp8(
+        out = dequantize_fp8(
             self._data,
             self._orig_dtype,
             self._granularity,
@@ -205,6 +225,11 @@ class QuantizedTensor(torch.Tensor):
             scale_inv=self._scale_inv,
             scaling_recipe=self._scaling_recipe,
         )
+        if self._granularity == ScalingGranularity.MX_BLOCKWISE and out.shape != self.shape:
+            # drop the zero padding of the quantised direction (the reference unpads the inner extent,
+            # quantized_tensor.py:605-611 there; the transposed copy's padding lies on the other extent)
+            out = out[..., : self.size(-2), : self.size(-1)].contiguous()
+        return out
 
     # ---- torch.compile / FSDP flattening ----------------------------------------------------------
     def __tensor_flatten__(self):
@@ -271,6 +296,12 @@ class QuantizedTensor(torch.Tensor):
         out_shape = torch.Size(target_shape)
         if out_shape == tensor.shape:
             return tensor._data, tensor._scale_inv, out_shape
+        if tensor._granularity == ScalingGranularity.MX_BLOCKWISE:
+            # the payload's inner extent is padded to 128 and every 32 of its elements own a scale byte: both
+            # follow the new leading extents (row-direction payloads only; :709-731 in the reference)
+            padded = _pad_inner_dim(tuple(target_shape), MXFP8_PADDING_ALIGN_SIZE)
+            scale_shape = (*padded[:-1], padded[-1] // tensor._block_size)
+            return op(tensor._data, *padded), op(tensor._scale_inv, *scale_shape), out_shape
         return op(tensor._data, *target_shape), tensor._scale_inv, out_shape
 
     def view(self, *shape) -> "QuantizedTensor":
@@ -297,6 +328,13 @@ class QuantizedTensor(torch.Tensor):
         shape[d0], shape[d1] = shape[d1], shape[d0]
         if t._granularity == ScalingGranularity.TENSORWISE:
             return t._like(transpose_2d_fp8(t._data), t._scale_inv, torch.Size(shape))
+        if t._granularity == ScalingGranularity.MX_BLOCKWISE:
+            # the column-direction copy of the same logical tensor, whose payload IS the transposed layout
+            # (:766-775 in the reference)
+            return cls.quantize(
+                t.dequantize(), t._dest_dtype, t._granularity, axis=-2, block_size=t._block_size,
+                scaling_recipe=t._scaling_recipe,
+            )
         return cls.quantize(
             t.dequantize().transpose(d0, d1).contiguous(),
             t._dest_dtype,
@@ -325,6 +363,9 @@ class QuantizedTensor(torch.Tensor):
                 target = torch.Size(args[1])
                 if t._granularity == ScalingGranularity.TENSORWISE:
                     return t._like(t._data.reshape(target), t._scale_inv, target)
+                if t._granularity == ScalingGranularity.MX_BLOCKWISE:
+                    data, scale_inv, shape = cls._view_data_and_scale_inv(t, target, torch.Tensor.reshape)
+                    return t._like(data, scale_inv, shape)
                 assert tuple(target) == tuple(t.shape), "only identity views are supported for scaled layouts"
                 return t._like(t._data, t._scale_inv, t.shape)
             if func is aten.clone.default:
@@ -403,7 +444,8 @@ def create_quantized_weight(
     """Quantise a weight once, optionally with its backward-direction companion
     (quantized_tensor.py:897-956 in the reference)."""
     g = quant_config.granularity
-    recipe = ScalingRecipe(use_2d_block=True) if g == ScalingGranularity.BLOCKWISE else ScalingRecipe()
+    blocked = g in (ScalingGranularity.BLOCKWISE, ScalingGranularity.MX_BLOCKWISE)
+    recipe = ScalingRecipe(use_2d_block=True) if blocked else ScalingRecipe()
     qw = QuantizedTensor.quantize(
         weight, dest_dtype, g, block_size=quant_config.block_size, scaling_recipe=recipe, axis=-1
     )
@@ -416,7 +458,8 @@ def create_quantized_weight(
                 weight.transpose(-2, -1).contiguous(), dest_dtype, g, block_size=quant_config.block_size,
                 scaling_recipe=recipe, axis=-2,
             )
-        elif g == ScalingGranularity.BLOCKWISE:
+        elif blocked:
+            # axis -2 of the same weight: for MX the payload of that copy is the transposed layout
             qw_t = QuantizedTensor.quantize(
                 weight, dest_dtype, g, block_size=quant_config.block_size, scaling_recipe=recipe, axis=-2
             )

@@ -185,17 +185,30 @@ class FP8GemmMXFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, b, a_t, b_t, trans_a, trans_b, out_dtype, config):
         assert trans_a == False and trans_b == True, "trans_a has to be False and trans_b has to be True"
-        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
-            raise NotImplementedError("MX_BLOCKWISE gemm_fp8 takes high-precision tensors in this build")
         dt = _get_fp8_dtype(config.format, True)
-        a_row, a_row_s, a_col, a_col_s = quantize_fp8_with_trans(
-            a.contiguous(), dt, config.granularity, block_size=config.block_size, scaling_recipe=ScalingRecipe()
-        )
-        recipe = ScalingRecipe(use_2d_block=True)
-        b_row, b_row_s, b_col, b_col_s = quantize_fp8_with_trans(
-            b.contiguous(), dt, config.granularity, block_size=config.block_size, scaling_recipe=recipe,
-            scaling_recipe_for_trans=recipe,
-        )
+
+        def both_directions(x, x_t, recipe):
+            """(row copy, its scales, transposed column copy, its scales) of one operand.  A pre-quantised
+            operand brings its row copy; its column copy comes from ``x_t`` or, as in the reference (:537-548),
+            from re-quantising the dequantised row copy along the other axis."""
+            if not isinstance(x, QuantizedTensor):
+                return quantize_fp8_with_trans(
+                    x.contiguous(), dt, config.granularity, block_size=config.block_size, scaling_recipe=recipe,
+                    scaling_recipe_for_trans=recipe,
+                )
+            check_quantized_tensor(x, config, axis=-1, scaling_recipe=recipe)
+            if x_t is None:
+                x_t = QuantizedTensor.quantize(
+                    x.dequantize(), x.real_dtype, config.granularity, axis=-2, block_size=config.block_size,
+                    scaling_recipe=recipe,
+                )
+            else:
+                assert isinstance(x_t, QuantizedTensor)
+                check_quantized_tensor(x_t, config, axis=-2, scaling_recipe=recipe)
+            return x.qdata, x.scale_inv, x_t.qdata, x_t.scale_inv
+
+        a_row, a_row_s, a_col, a_col_s = both_directions(a, a_t, ScalingRecipe())
+        b_row, b_row_s, b_col, b_col_s = both_directions(b, b_t, ScalingRecipe(use_2d_block=True))
         out = gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, out_dtype)  # [M, K_pad] x [N, K_pad]^T
         ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s)
         ctx.out_dtype, ctx.config = out_dtype, config

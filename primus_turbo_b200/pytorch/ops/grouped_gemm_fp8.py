@@ -227,17 +227,35 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
     and the numbers are the same."""
 
     @staticmethod
-    def forward(ctx, a, b, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+    def forward(ctx, a, b, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
         assert config.granularity == ScalingGranularity.MX_BLOCKWISE
         assert a.ndim == 2 and b.ndim == 3
         assert trans_b, "MXFP8 grouped GEMM only supports trans_b=True (NT layout)."
-        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
-            raise NotImplementedError("MX_BLOCKWISE grouped_gemm_fp8 takes high-precision tensors in this build")
+        if isinstance(a, QuantizedTensor):
+            # the reference's grouped MX activation tensor carries a row copy padded to 32 rows per group, which
+            # its GEMM reads through padded offsets; this build's GEMM reads the unpadded row copy it makes itself
+            raise NotImplementedError("MX_BLOCKWISE grouped_gemm_fp8 takes a high-precision activation in this build")
         dt = _get_fp8_dtype(config.format, True)
         a_row, a_row_s, a_col, a_col_s, _, _, _, col_offs = grouped_quantize_mxfp8_impl(
             _contig(a), dt, config.block_size, group_lens, group_offs, False, False, row_align=1
         )
-        b_row, b_row_s, b_col, b_col_s = quantize_mxfp8_impl(_contig(b), dt, None, config.block_size, True, True, True)
+        if isinstance(b, QuantizedTensor):
+            # a weight quantised ahead of time (32x32 tiles, axis -1); its column copy comes from ``b_t`` or from
+            # re-quantising the dequantised row copy along the other axis, as in the reference (:668-692)
+            recipe = ScalingRecipe(use_2d_block=True)
+            assert not b._is_grouped_tensor, "B QuantizedTensor input must not be a grouped tensor"
+            check_quantized_tensor(b, config, axis=-1, scaling_recipe=recipe)
+            if b_t is None:
+                b_t = QuantizedTensor.quantize(
+                    b.dequantize(), b.real_dtype, config.granularity, axis=-2, block_size=config.block_size,
+                    scaling_recipe=recipe,
+                )
+            else:
+                assert isinstance(b_t, QuantizedTensor)
+                check_quantized_tensor(b_t, config, axis=-2, scaling_recipe=recipe)
+            b_row, b_row_s, b_col, b_col_s = b.qdata, b.scale_inv, b_t.qdata, b_t.scale_inv
+        else:
+            b_row, b_row_s, b_col, b_col_s = quantize_mxfp8_impl(_contig(b), dt, None, config.block_size, True, True, True)
         sms = num_cu or 0
         out = grouped_gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, group_offs, out_dtype, sms)
         ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s, group_lens, group_offs)
@@ -256,7 +274,7 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
         grad_a = grouped_gemm_mxfp8_impl(g_row, g_row_s, b_col, b_col_s, group_offs, ctx.out_dtype, ctx.sms)
         # wgrad: grad_b[g] = grad_out_g^T . a_g = g_col [N, rows] x (a_col [K, rows])^T over the group's padded rows
         grad_b = grouped_gemm_mxfp8_variable_k_impl(g_col, g_col_s, a_col, a_col_s, col_offs, ctx.out_dtype, ctx.sms)
-        return grad_a, grad_b, None, None, None, None, None, None
+        return grad_a, grad_b, None, None, None, None, None, None, None
 
 
 def grouped_gemm_fp8(
@@ -296,5 +314,5 @@ def grouped_gemm_fp8(
         # and dgrad read the same 128x128-block payload)
         return FP8GroupedGemmBlockFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     if config.granularity == ScalingGranularity.MX_BLOCKWISE:
-        return FP8GroupedGemmMXFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
+        return FP8GroupedGemmMXFunc.apply(a_data, b_data, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

@@ -98,3 +98,116 @@ def test_grouped_gemm_call_sequence(recorded_calls, granularity, rows):
     out.backward(torch.zeros((rows, N), dtype=torch.bfloat16))
     assert _names(recorded_calls) == backward
     assert a.grad.shape == (rows, K) and w.grad.shape == (G, N, K)
+
+
+# ---- MXFP8 payloads in QuantizedTensor ----------------------------------------------------------------------
+MX_MODULES = MODULES + ("primus_turbo_b200.pytorch.ops.gemm_fp8",)
+MX = ScalingGranularity.MX_BLOCKWISE
+
+
+def _mx_cfg():
+    return Float8QuantConfig(granularity=MX, block_size=32, scale_dtype=ScaleDtype.E8M0)
+
+
+def test_mx_quantized_tensor_layouts(recorded_calls):
+    """Logical shape outside, padded payload inside: axis -1 keeps rows and pads the inner extent to 128, axis -2
+    holds the transposed copy; dequantize drops the padding; a view (same number of dimensions) re-splits the leading
+    extents of payload and scale bytes alike; ``.t()`` is the other-direction copy of the same logical tensor."""
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingRecipe
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
+
+    x = torch.zeros((96, 160), dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="scaling_recipe must be provided"):
+        QuantizedTensor.quantize(x, E4, MX, axis=-1, block_size=32)
+    row = QuantizedTensor.quantize(x, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe())
+    assert row.shape == (96, 160) and row.qdata.shape == (96, 256) and row.scale_inv.shape == (96, 8)
+    assert row.scale_inv.dtype == torch.float8_e8m0fnu and row.quantized_axis == -1
+    col = QuantizedTensor.quantize(x, E4, MX, axis=-2, block_size=32, scaling_recipe=ScalingRecipe())
+    assert col.shape == (96, 160) and col.qdata.shape == (160, 128) and col.scale_inv.shape == (160, 4)
+    assert row.dequantize().shape == (96, 160) and col.dequantize().shape == (96, 160)
+    del recorded_calls[:]
+    t = row.t()
+    assert t.quantized_axis == -2 and t.qdata.shape == (160, 128) and t.shape == (96, 160)
+    assert _names(recorded_calls) == ["ptb_dequant_mxfp8", "ptb_quant_mxfp8"]
+    w = torch.zeros((3, 64, 128), dtype=torch.bfloat16)
+    qw = QuantizedTensor.quantize(w, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe(use_2d_block=True))
+    assert qw.qdata.shape == (3, 64, 128) and qw.scale_inv.shape == (3, 64, 4)
+    v = qw.view(6, 32, 128)  # same number of dimensions, leading extents re-split
+    assert v.shape == (6, 32, 128) and v.qdata.shape == (6, 32, 128) and v.scale_inv.shape == (6, 32, 4)
+    x3 = QuantizedTensor.quantize(torch.zeros((2, 48, 160), dtype=torch.bfloat16), E4, MX, axis=-1, block_size=32,
+                                  scaling_recipe=ScalingRecipe())
+    v = x3.reshape(4, 24, 160)  # the payload's inner extent stays padded to 128
+    assert v.shape == (4, 24, 160) and v.qdata.shape == (4, 24, 256) and v.scale_inv.shape == (4, 24, 8)
+    qw_t = QuantizedTensor.quantize(w, E4, MX, axis=-2, block_size=32, scaling_recipe=ScalingRecipe(use_2d_block=True))
+    assert qw_t.qdata.shape == (3, 128, 128) and qw_t.scale_inv.shape == (3, 128, 4)
+    assert qw_t.dequantize().shape == (3, 64, 128)
+
+
+def test_mx_create_quantized_weight(recorded_calls):
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingRecipe
+    from primus_turbo_b200.pytorch.core.quantized_tensor import create_quantized_weight
+
+    w = torch.zeros((256, 512), dtype=torch.bfloat16, requires_grad=True)
+    qw, qw_t = create_quantized_weight(w, E4, _mx_cfg(), need_weight_transpose_cache=True)
+    assert qw.scaling_recipe == ScalingRecipe(use_2d_block=True) == qw_t.scaling_recipe
+    assert qw.quantized_axis == -1 and qw_t.quantized_axis == -2
+    assert qw.qdata.shape == (256, 512) and qw_t.qdata.shape == (512, 256)
+    # both copies are 32x32-tile quantisations: the 2-D flag is argument 9 (row) / 10 (column) of the entry point
+    assert [(c[0], c[1][9], c[1][10]) for c in recorded_calls] == [("ptb_quant_mxfp8", 1, 1)] * 2
+
+
+@pytest.mark.parametrize("with_transposed", [False, True])
+def test_mx_gemm_with_quantized_operands(monkeypatch, recorded_calls, with_transposed):
+    """Pre-quantised operands bring their row copies; the column copies come from the pair's second member or from
+    a dequantise -> re-quantise along the other axis (the reference's schedule)."""
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingRecipe
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor, QuantizedTensorPair
+
+    import importlib
+
+    gemm = importlib.import_module("primus_turbo_b200.pytorch.ops.gemm_fp8")
+    impl = sys.modules["primus_turbo_b200.pytorch.kernels.gemm_impl"]
+    for mod in (gemm, impl):
+        for n in ("require_cuda", "stream_of"):
+            if hasattr(mod, n):
+                monkeypatch.setattr(mod, n, (lambda *t: None) if n == "require_cuda" else (lambda t: 0))
+    M, N, K = 256, 352, 160
+    a = torch.zeros((M, K), dtype=torch.bfloat16, requires_grad=True)
+    b = torch.zeros((N, K), dtype=torch.bfloat16, requires_grad=True)
+    ra, rb = ScalingRecipe(), ScalingRecipe(use_2d_block=True)
+    qa = QuantizedTensor.quantize(a, E4, MX, axis=-1, block_size=32, scaling_recipe=ra)
+    qb = QuantizedTensor.quantize(b, E4, MX, axis=-1, block_size=32, scaling_recipe=rb)
+    qa_t = QuantizedTensor.quantize(a, E4, MX, axis=-2, block_size=32, scaling_recipe=ra) if with_transposed else None
+    qb_t = QuantizedTensor.quantize(b, E4, MX, axis=-2, block_size=32, scaling_recipe=rb) if with_transposed else None
+    del recorded_calls[:]
+    out = gemm.gemm_fp8(QuantizedTensorPair(qa, qa_t), QuantizedTensorPair(qb, qb_t), False, True, torch.bfloat16, _mx_cfg())
+    assert out.shape == (M, N)
+    requant = [] if with_transposed else ["ptb_dequant_mxfp8", "ptb_quant_mxfp8"] * 2
+    assert _names(recorded_calls) == requant + ["ptb_gemm_mxfp8"]
+    del recorded_calls[:]
+    out.backward(torch.zeros((M, N), dtype=torch.bfloat16))
+    assert _names(recorded_calls) == ["ptb_quant_mxfp8", "ptb_gemm_mxfp8", "ptb_gemm_mxfp8"]
+    assert qa.grad.shape == (M, K) and qb.grad.shape == (N, K)
+    # a row-direction operand handed over as the column copy is refused
+    with pytest.raises(AssertionError, match="quantized_axis"):
+        gemm.gemm_fp8(QuantizedTensorPair(qa, qa), QuantizedTensorPair(qb, qb_t), False, True, torch.bfloat16, _mx_cfg())
+
+
+def test_mx_grouped_gemm_with_quantized_weight(recorded_calls):
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensorPair, create_quantized_weight
+
+    grouped = sys.modules["primus_turbo_b200.pytorch.ops.grouped_gemm_fp8"]
+    G, K, N, rows = 2, 512, 384, 200
+    w = torch.zeros((G, N, K), dtype=torch.bfloat16, requires_grad=True)
+    qw, qw_t = create_quantized_weight(w, E4, _mx_cfg(), need_weight_transpose_cache=True)
+    lens = torch.tensor([rows, 0], dtype=torch.int64)
+    offs = torch.cat([lens.new_zeros(1), lens.cumsum(0)])
+    a = torch.zeros((rows, K), dtype=torch.bfloat16, requires_grad=True)
+    del recorded_calls[:]
+    out = grouped.grouped_gemm_fp8(a, QuantizedTensorPair(qw, qw_t), lens, offs, config=_mx_cfg())
+    assert out.shape == (rows, N)
+    assert _names(recorded_calls) == ["ptb_quant_mxfp8_grouped", "ptb_grouped_gemm_mxfp8"]
+    del recorded_calls[:]
+    out.backward(torch.zeros((rows, N), dtype=torch.bfloat16))
+    assert _names(recorded_calls) == ["ptb_quant_mxfp8_grouped", "ptb_grouped_gemm_mxfp8", "ptb_grouped_gemm_mxfp8_variable_k"]
+    assert a.grad.shape == (rows, K) and qw.grad.shape == (G, N, K)
