@@ -5,8 +5,9 @@
  * (passed as void*, i.e. a cudaStream_t).  The caller allocates every output and workspace.  All
  * work is enqueued on the given stream; no call synchronises the host with the device (except
  * ptb_gemm_status and ptb_copy_segments_status, which read one word back).  Calls are re-entrant.
- * The library keeps no state between calls, with three stated exceptions: (1) ptb_quant_fp8_rowwise_noalloc reduces into one
- * fixed device array that all of its calls share; (2) the GEMM kernels record a wait that ran out
+ * The library keeps no state between calls, with three stated exceptions:
+ * (1) ptb_quant_fp8_rowwise_noalloc reduces into one fixed device array that all of its calls
+ * share; (2) the GEMM kernels record a wait that ran out
  * in one device word per GPU, shared by all streams and read with ptb_gemm_status, and the peer
  * copies do the same for a bad rank number or a flag wait that ran out (ptb_copy_segments_status);
  * (3) per-device one-time set-up (kernel attributes, the address of that array) is cached in the
