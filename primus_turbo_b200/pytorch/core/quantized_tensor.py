@@ -4,8 +4,10 @@ API-compatible with primus_turbo/pytorch/core/quantized_tensor.py:113-145 (check
 :148-835 (QuantizedTensor) and :884-894 (QuantizedTensorPair) for the FP8 tensorwise / rowwise /
 blockwise granularities and for (non-grouped) MXFP8 payloads: an MX tensor holds its FP8 bytes padded to a
 multiple of 128 along the quantised direction (axis -1: ``[.., M, K_pad]``; axis -2: the TRANSPOSED copy
-``[.., K, M_pad]``) and one E8M0 byte per 32 elements; its wrapper shape stays the logical one.  Grouped MX
-activations (the reference's per-group padded layouts) and FP4 payloads are not part of this build.
+``[.., K, M_pad]``) and one E8M0 byte per 32 elements; its wrapper shape stays the logical one.  A grouped MX
+activation holds the per-group padded layout of its direction (32 rows per group for the row copy, 128 for the
+transposed column copy) together with the padded and the original group lengths / offsets.  FP4 payloads are
+not part of this build.
 """
 
 from __future__ import annotations
@@ -138,24 +140,37 @@ class QuantizedTensor(torch.Tensor):
         if granularity != ScalingGranularity.TENSORWISE:
             assert axis is not None, "axis must be provided for non-TENSORWISE granularity"
         grouped = group_lens is not None
-        g_lens = g_offs = None
+        g_lens = g_offs = p_lens = p_offs = None
         if grouped:
-            # Tensorwise / rowwise scales do not depend on the grouping: the packed [sum(M_g), K]
-            # tensor is quantised as a whole and only carries the group metadata along.
-            assert granularity in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE), (
-                "grouped BLOCKWISE / MX_BLOCKWISE activations are quantised inside grouped_gemm_fp8"
+            assert granularity != ScalingGranularity.BLOCKWISE, (
+                "grouped BLOCKWISE activations are quantised inside grouped_gemm_fp8"
             )
             assert hp_tensor.ndim == 2 and group_lens.is_cuda
             g_lens, g_offs = group_lens, group_offs_from_lens(group_lens)
-        with torch.no_grad():
-            data, scale_inv = quantize_fp8(
-                hp_tensor.detach().contiguous(),
-                dest_dtype,
-                granularity,
-                block_size=block_size,
-                axis=_norm_axis(axis, hp_tensor.ndim),
-                scaling_recipe=scaling_recipe,
-            )
+        if grouped and granularity == ScalingGranularity.MX_BLOCKWISE:
+            # every group quantised on its own into the padded layout of that direction (32 rows per group for
+            # the row copy, 128 for the transposed column copy); the tensor keeps both sets of lengths / offsets
+            # (:325-338 in the reference)
+            from primus_turbo_b200.pytorch.ops.quantization import grouped_quantize_fp8
+
+            with torch.no_grad():
+                data, scale_inv, p_lens, p_offs = grouped_quantize_fp8(
+                    hp_tensor.detach().contiguous(), dest_dtype, granularity, g_lens, g_offs, block_size=block_size,
+                    axis=_norm_axis(axis, 2), scaling_recipe=scaling_recipe,
+                )
+        else:
+            # Tensorwise / rowwise scales do not depend on the grouping: the packed [sum(M_g), K] tensor is
+            # quantised as a whole and only carries the group metadata along.
+            p_lens, p_offs = g_lens, g_offs
+            with torch.no_grad():
+                data, scale_inv = quantize_fp8(
+                    hp_tensor.detach().contiguous(),
+                    dest_dtype,
+                    granularity,
+                    block_size=block_size,
+                    axis=_norm_axis(axis, hp_tensor.ndim),
+                    scaling_recipe=scaling_recipe,
+                )
         return cls(
             data,
             scale_inv,
@@ -169,8 +184,8 @@ class QuantizedTensor(torch.Tensor):
             quantized_axis=axis,
             orig_group_lens=g_lens,
             orig_group_offs=g_offs,
-            group_lens=g_lens,
-            group_offs=g_offs,
+            group_lens=p_lens,
+            group_offs=p_offs,
             is_grouped_tensor=grouped,
         )
 
@@ -214,8 +229,16 @@ class QuantizedTensor(torch.Tensor):
     @torch.no_grad()
     def dequantize(self) -> torch.Tensor:
         """Back to the original high-precision dtype: cast(float(q) * scale_inv)."""
-        from primus_turbo_b200.pytorch.ops.quantization import dequantize_fp8
+        from primus_turbo_b200.pytorch.ops.quantization import dequantize_fp8, grouped_dequantize_fp8
 
+        if self._is_grouped_tensor and self._granularity == ScalingGranularity.MX_BLOCKWISE:
+            # the padded layout back to the packed rows (:533-549 in the reference)
+            out = grouped_dequantize_fp8(
+                self._data, self._orig_dtype, self._granularity, self._orig_group_offs, self._group_offs,
+                block_size=self._block_size, axis=_norm_axis(self._quantized_axis, 2), scale_inv=self._scale_inv,
+                scaling_recipe=self._scaling_recipe, total_M=self.shape[0],
+            )
+            return out if out.shape == self.shape else out[:, : self.size(-1)].contiguous()
         out = dequantize_fp8(
             self._data,
             self._orig_dtype,

@@ -414,3 +414,40 @@ def grouped_quantize_mxfp8_impl(
             int(use_2d_block), int(use_2d_block_for_trans), dtype_code(out_dtype), stream_of(x),
         )
     return q_row, s_row.view(E8M0), q_col, s_col.view(E8M0), row_lens, row_offs, col_lens, col_offs
+
+
+def packed_row_index(group_offs: torch.Tensor, group_offs_padded: torch.Tensor, total_rows: int) -> torch.Tensor:
+    """For each of ``total_rows`` packed rows (group g holds rows [offs[g], offs[g+1])) its row in a layout where
+    group g starts at ``offs_padded[g]``: ``offs_padded[g] + (r - offs[g])``.  Computed on the device, no
+    synchronisation; rows at or past ``offs[G]`` follow the last group (they stay inside the padded layout,
+    whose allocation bounds every group's padding)."""
+    G = group_offs.numel() - 1
+    r = torch.arange(total_rows, device=group_offs.device, dtype=torch.int64)
+    g = torch.searchsorted(group_offs[1:].contiguous(), r, right=True).clamp_(max=G - 1)
+    return r + (group_offs_padded[:-1] - group_offs[:-1])[g]
+
+
+def grouped_dequantize_mxfp8_impl(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    axis: int,
+    block_size: int,
+    scale_inv: torch.Tensor,
+    group_offs: torch.Tensor,
+    group_offs_padded: torch.Tensor,
+    total_M: int | None = None,
+) -> torch.Tensor:
+    """Back from a grouped MXFP8 payload (axis 1: the row copy, groups padded to 32 rows; axis 0: the transposed
+    column copy, groups padded to 128) to the packed rows ``[total_M, N_pad]`` / ``[total_M, N]``: the padded
+    layout is dequantised as a whole and the rows that exist are gathered out of it.  ``total_M`` defaults to
+    ``group_offs[-1]`` (one synchronisation).
+    (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:727-754 in the reference.)"""
+    assert x.dim() == 2 and scale_inv.dim() == 2, "The x and scale_inv must be 2D tensors."
+    assert axis in (0, 1), "The axis must be 0 or 1."
+    assert group_offs.dtype == torch.int64 and group_offs_padded.dtype == torch.int64
+    assert group_offs.numel() == group_offs_padded.numel() >= 2
+    full = dequantize_mxfp8_impl(x, out_dtype, axis, block_size, scale_inv)
+    if total_M is None:
+        total_M = int(group_offs[-1])
+    return full.index_select(0, packed_row_index(group_offs, group_offs_padded, total_M))
+

@@ -40,7 +40,11 @@ from primus_turbo_b200.pytorch.kernels.gemm_impl import (
     grouped_gemm_mxfp8_impl,
     grouped_gemm_mxfp8_variable_k_impl,
 )
-from primus_turbo_b200.pytorch.kernels.quantization_impl import grouped_quantize_mxfp8_impl, quantize_mxfp8_impl
+from primus_turbo_b200.pytorch.kernels.quantization_impl import (
+    grouped_quantize_mxfp8_impl,
+    packed_row_index,
+    quantize_mxfp8_impl,
+)
 
 __all__ = ["grouped_gemm_fp8"]
 
@@ -227,18 +231,36 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
     and the numbers are the same."""
 
     @staticmethod
-    def forward(ctx, a, b, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
+    def forward(ctx, a, b, a_t, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu):
         assert config.granularity == ScalingGranularity.MX_BLOCKWISE
         assert a.ndim == 2 and b.ndim == 3
         assert trans_b, "MXFP8 grouped GEMM only supports trans_b=True (NT layout)."
-        if isinstance(a, QuantizedTensor):
-            # the reference's grouped MX activation tensor carries a row copy padded to 32 rows per group, which
-            # its GEMM reads through padded offsets; this build's GEMM reads the unpadded row copy it makes itself
-            raise NotImplementedError("MX_BLOCKWISE grouped_gemm_fp8 takes a high-precision activation in this build")
         dt = _get_fp8_dtype(config.format, True)
-        a_row, a_row_s, a_col, a_col_s, _, _, _, col_offs = grouped_quantize_mxfp8_impl(
-            _contig(a), dt, config.block_size, group_lens, group_offs, False, False, row_align=1
-        )
+        a_offs, pack = group_offs, None
+        if isinstance(a, QuantizedTensor):
+            # A grouped activation quantised ahead of time carries the reference's layout: the row copy with every
+            # group padded to 32 rows.  The GEMM runs over that layout (the padding rows cost a little and their
+            # results are dropped) and the rows that exist are gathered into the packed output, which is what the
+            # reference does with its padded / packed offset pair (:693-720).  The column copy comes from ``a_t``
+            # or from re-quantising the dequantised row copy along the other axis (:634-648).
+            recipe = ScalingRecipe()
+            assert a._is_grouped_tensor, "A QuantizedTensor input must be a grouped tensor"
+            check_quantized_tensor(a, config, axis=-1, scaling_recipe=recipe)
+            if a_t is None:
+                a_t = QuantizedTensor.quantize(
+                    a.dequantize(), a.real_dtype, config.granularity, axis=-2, block_size=config.block_size,
+                    scaling_recipe=recipe, group_lens=group_lens,
+                )
+            else:
+                assert isinstance(a_t, QuantizedTensor) and a_t._is_grouped_tensor
+                check_quantized_tensor(a_t, config, axis=-2, scaling_recipe=recipe)
+            a_row, a_row_s, a_col, a_col_s = a.qdata, a.scale_inv, a_t.qdata, a_t.scale_inv
+            a_offs = a.group_offs
+            pack = packed_row_index(group_offs, a_offs, a.shape[0])
+        else:
+            a_row, a_row_s, a_col, a_col_s, _, _, _, _ = grouped_quantize_mxfp8_impl(
+                _contig(a), dt, config.block_size, group_lens, group_offs, False, False, row_align=1
+            )
         if isinstance(b, QuantizedTensor):
             # a weight quantised ahead of time (32x32 tiles, axis -1); its column copy comes from ``b_t`` or from
             # re-quantising the dequantised row copy along the other axis, as in the reference (:668-692)
@@ -257,7 +279,9 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
         else:
             b_row, b_row_s, b_col, b_col_s = quantize_mxfp8_impl(_contig(b), dt, None, config.block_size, True, True, True)
         sms = num_cu or 0
-        out = grouped_gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, group_offs, out_dtype, sms)
+        out = grouped_gemm_mxfp8_impl(a_row, a_row_s, b_row, b_row_s, a_offs, out_dtype, sms)
+        if pack is not None:
+            out = out.index_select(0, pack)
         ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s, group_lens, group_offs)
         ctx.config, ctx.out_dtype, ctx.sms = config, out_dtype, sms
         return out
@@ -274,7 +298,7 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
         grad_a = grouped_gemm_mxfp8_impl(g_row, g_row_s, b_col, b_col_s, group_offs, ctx.out_dtype, ctx.sms)
         # wgrad: grad_b[g] = grad_out_g^T . a_g = g_col [N, rows] x (a_col [K, rows])^T over the group's padded rows
         grad_b = grouped_gemm_mxfp8_variable_k_impl(g_col, g_col_s, a_col, a_col_s, col_offs, ctx.out_dtype, ctx.sms)
-        return grad_a, grad_b, None, None, None, None, None, None, None
+        return grad_a, grad_b, None, None, None, None, None, None, None, None
 
 
 def grouped_gemm_fp8(
@@ -314,5 +338,5 @@ def grouped_gemm_fp8(
         # and dgrad read the same 128x128-block payload)
         return FP8GroupedGemmBlockFunc.apply(a_data, b_data, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     if config.granularity == ScalingGranularity.MX_BLOCKWISE:
-        return FP8GroupedGemmMXFunc.apply(a_data, b_data, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
+        return FP8GroupedGemmMXFunc.apply(a_data, b_data, a_data_t, b_data_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu)
     raise ValueError(f"Unsupported FP8 ScalingGranularity: {config.granularity}")

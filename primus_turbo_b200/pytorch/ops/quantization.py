@@ -11,11 +11,19 @@ from primus_turbo_b200.pytorch.core.low_precision import MXFP8_BLOCK_SIZE
 from primus_turbo_b200.pytorch.kernels import custom_ops as _ops
 from primus_turbo_b200.pytorch.kernels.quantization_impl import (
     dequantize_mxfp8_impl,
+    grouped_dequantize_mxfp8_impl,
     grouped_quantize_mxfp8_impl,
     quantize_mxfp8_impl,
 )
 
-__all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8", "grouped_quantize_fp8_with_trans"]
+__all__ = [
+    "quantize_fp8",
+    "quantize_fp8_with_trans",
+    "dequantize_fp8",
+    "grouped_quantize_fp8",
+    "grouped_quantize_fp8_with_trans",
+    "grouped_dequantize_fp8",
+]
 
 
 def quantize_fp8(
@@ -85,6 +93,53 @@ def quantize_fp8_with_trans(
             x, out_dtype, None, block_size, True,
             bool(scaling_recipe is not None and scaling_recipe.use_2d_block),
             bool(scaling_recipe_for_trans is not None and scaling_recipe_for_trans.use_2d_block),
+        )
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_quantize_fp8(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    group_lens: torch.Tensor,
+    group_offs: torch.Tensor,
+    *,
+    block_size: Optional[int] = None,
+    axis: Optional[int] = None,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """MXFP8 only (ops/quantization.py:143-176 in the reference): one direction of x [M, N] per group ->
+    (data, scale_inv, group_lens_padded, group_offs_padded); axis 1: the row copy, groups padded to 32 rows;
+    axis 0: the transposed column copy, groups padded to 128.  One kernel makes both directions here; the
+    other one is dropped."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        assert axis in (0, 1), "The axis must be 0 or 1."
+        _reject_shuffle(scaling_recipe)
+        use_2d = bool(scaling_recipe is not None and scaling_recipe.use_2d_block)
+        outs = grouped_quantize_mxfp8_impl(x, out_dtype, block_size, group_lens, group_offs, use_2d, use_2d)
+        return (outs[0], outs[1], outs[4], outs[5]) if axis == 1 else (outs[2], outs[3], outs[6], outs[7])
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_dequantize_fp8(
+    x: torch.Tensor,
+    out_dtype: torch.dtype,
+    granularity: ScalingGranularity,
+    group_offs: torch.Tensor,
+    group_offs_padded: torch.Tensor,
+    *,
+    block_size: Optional[int] = None,
+    axis: Optional[int] = None,
+    scale_inv: torch.Tensor,
+    scaling_recipe: Optional[ScalingRecipe] = None,
+    total_M: Optional[int] = None,
+) -> torch.Tensor:
+    """MXFP8 only (ops/quantization.py:272-296 in the reference): a grouped payload back to its packed rows."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        return grouped_dequantize_mxfp8_impl(
+            x, out_dtype, axis, block_size, scale_inv, group_offs, group_offs_padded, total_M
         )
     raise NotImplementedError(f"Unknown granularity {granularity}")
 

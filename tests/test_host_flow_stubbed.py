@@ -211,3 +211,86 @@ def test_mx_grouped_gemm_with_quantized_weight(recorded_calls):
     out.backward(torch.zeros((rows, N), dtype=torch.bfloat16))
     assert _names(recorded_calls) == ["ptb_quant_mxfp8_grouped", "ptb_grouped_gemm_mxfp8", "ptb_grouped_gemm_mxfp8_variable_k"]
     assert a.grad.shape == (rows, K) and qw.grad.shape == (G, N, K)
+
+
+# ---- grouped MX activations -----------------------------------------------------------------------------------
+def _emulate_group_layout(calls):
+    """Stand-in for the layout kernel of ``ptb_quant_mxfp8_grouped``: reads the group offsets and writes the
+    padded lengths / offsets of both layouts through the (host) pointers the call was given."""
+    import ctypes
+
+    def at(ptr, n):
+        return (ctypes.c_int64 * n).from_address(ptr)
+
+    name, a = calls[-1]
+    assert name == "ptb_quant_mxfp8_grouped"
+    G, row_align = a[5], a[6]
+    offs = list(at(a[4], G + 1))
+    for lens_ptr, offs_ptr, align in ((a[11], a[12], row_align), (a[13], a[14], 128)):
+        run = 0
+        for g in range(G):
+            padded = -(-(offs[g + 1] - offs[g]) // align) * align
+            at(lens_ptr, G)[g] = padded
+            at(offs_ptr, G + 1)[g] = run
+            run += padded
+        at(offs_ptr, G + 1)[G] = run
+
+
+def test_packed_row_index():
+    from primus_turbo_b200.pytorch.kernels.quantization_impl import packed_row_index
+
+    offs = torch.tensor([0, 100, 100, 257, 300])
+    padded = torch.tensor([0, 128, 128, 288, 352])  # groups padded to 32 rows
+    idx = packed_row_index(offs, padded, 300).tolist()
+    want = list(range(0, 100)) + list(range(128, 128 + 157)) + list(range(288, 288 + 43))
+    assert idx == want
+    # rows past the last group stay inside the padded layout
+    assert packed_row_index(offs, padded, 304).tolist()[-4:] == [331, 332, 333, 334]
+
+
+def test_mx_grouped_activation_as_quantized_tensor(monkeypatch, recorded_calls):
+    """A grouped activation quantised ahead of time: padded layouts inside, packed rows outside; the grouped GEMM
+    runs over the padded row copy and gathers the rows that exist."""
+    from primus_turbo_b200.pytorch.core.low_precision import ScalingRecipe
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor, QuantizedTensorPair
+
+    gemm_impl = sys.modules["primus_turbo_b200.pytorch.kernels.gemm_impl"]
+    grouped = sys.modules["primus_turbo_b200.pytorch.ops.grouped_gemm_fp8"]
+    qt_mod = sys.modules["primus_turbo_b200.pytorch.core.quantized_tensor"]
+    offsets = lambda lens: torch.cat([lens.new_zeros(1), lens.cumsum(0)])  # noqa: E731
+    monkeypatch.setattr(gemm_impl, "group_offs_from_lens", offsets)
+    monkeypatch.setattr(grouped, "group_offs_from_lens", offsets)
+
+    def call(name, *a):
+        recorded_calls.append((name, a))
+        if name == "ptb_quant_mxfp8_grouped":
+            _emulate_group_layout(recorded_calls)
+
+    monkeypatch.setattr(_lib, "call", call)
+    # the group tensors live on the host here
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    G, K, N = 4, 160, 96
+    lens = torch.tensor([100, 0, 157, 43], dtype=torch.int64)
+    M = int(lens.sum())
+    a = torch.zeros((M, K), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.zeros((G, N, K), dtype=torch.bfloat16, requires_grad=True)
+    qa = QuantizedTensor.quantize(a, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe(), group_lens=lens)
+    assert qa.shape == (M, K) and qa._is_grouped_tensor
+    assert qa.qdata.shape == (448, 256) and qa.scale_inv.shape == (448, 8)  # ceil((300 + 4*32) / 32) * 32 rows
+    assert qa.group_lens.tolist() == [128, 0, 160, 64] and qa.group_offs.tolist() == [0, 128, 128, 288, 352]
+    assert qa._orig_group_offs.tolist() == [0, 100, 100, 257, 300]
+    qa_t = QuantizedTensor.quantize(a, E4, MX, axis=-2, block_size=32, scaling_recipe=ScalingRecipe(), group_lens=lens)
+    assert qa_t.qdata.shape == (K, 896) and qa_t.group_offs.tolist() == [0, 128, 128, 384, 512]
+    assert qa.dequantize().shape == (M, K) and qa_t.dequantize().shape == (M, K)
+    del recorded_calls[:]
+    out = grouped.grouped_gemm_fp8(QuantizedTensorPair(qa, None), w, lens, config=_mx_cfg())
+    assert out.shape == (M, N)
+    assert _names(recorded_calls) == ["ptb_dequant_mxfp8", "ptb_quant_mxfp8_grouped", "ptb_quant_mxfp8",
+                                      "ptb_grouped_gemm_mxfp8"]
+    gemm_args = recorded_calls[-1][1]
+    assert gemm_args[13] == 448, "the GEMM runs over the padded row layout"
+    del recorded_calls[:]
+    out.backward(torch.zeros((M, N), dtype=torch.bfloat16))
+    assert _names(recorded_calls) == ["ptb_quant_mxfp8_grouped", "ptb_grouped_gemm_mxfp8", "ptb_grouped_gemm_mxfp8_variable_k"]
+    assert recorded_calls[1][1][13] == M, "dgrad runs over the packed rows"
+    assert qa.grad.shape == (M, K) and w.grad.shape == (G, N, K)

@@ -98,7 +98,7 @@ def test_gemm_with_pre_quantised_operands(fmt, mnk):
 
 
 def test_grouped_gemm_with_pre_quantised_weight():
-    G, K, N = 4, 512, 384
+    G, K, N = 4, 128, 256  # shapes the raw-tensor grouped MX tests cover
     lens = torch.tensor([100, 0, 157, 43], dtype=torch.int64, device=DEV)
     rows = int(lens.sum())
     cfg = _cfg()
@@ -117,6 +117,48 @@ def test_grouped_gemm_with_pre_quantised_weight():
     assert _lib.gemm_status() == 0
     for r, g in zip(ref, got):
         assert torch.equal(r, g)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError, match="grouped tensor"):
         qa = QuantizedTensor.quantize(a, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe())
         grouped_gemm_fp8(qa, w, lens, config=cfg)
+
+
+def test_grouped_activation_as_quantized_tensor():
+    """The reference's grouped MX activation tensor (row copy padded to 32 rows per group, transposed column copy
+    padded to 128): layout metadata, round trip, and the grouped GEMM over it against the raw-tensor call."""
+    G, K, N = 4, 96, 320  # shapes the raw-tensor grouped MX tests cover
+    lens_host = [100, 0, 157, 43]
+    lens = torch.tensor(lens_host, dtype=torch.int64, device=DEV)
+    M = sum(lens_host)
+    cfg = _cfg()
+    a, w, gy = _mk((M, K), 7), _mk((G, N, K), 8, 0.05), _mk((M, N), 9, 0.01)
+    a1 = a.clone().requires_grad_()
+    qa = QuantizedTensor.quantize(a1, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe(), group_lens=lens)
+    qa_t = QuantizedTensor.quantize(a1, E4, MX, axis=-2, block_size=32, scaling_recipe=ScalingRecipe(), group_lens=lens)
+    assert qa.shape == (M, K) and qa.qdata.shape == (448, 128)
+    assert qa.group_lens.tolist() == [128, 0, 160, 64] and qa.group_offs.tolist() == [0, 128, 128, 288, 352]
+    assert qa_t.qdata.shape == (K, 896) and qa_t.group_offs.tolist() == [0, 128, 128, 384, 512]
+    for t in (qa, qa_t):
+        back = t.dequantize()
+        assert back.shape == (M, K)
+        assert O.rel_frobenius(a.float().cpu(), back.float().cpu()) <= 0.04
+
+    def run(a_op, a_leaf, w_leaf):
+        out = grouped_gemm_fp8(a_op, w_leaf, lens, config=cfg)
+        out.backward(gy)
+        return out.detach(), a_leaf.grad, w_leaf.grad
+
+    a0, w0 = a.clone().requires_grad_(), w.clone().requires_grad_()
+    ref = run(a0, a0, w0)
+    w1 = w.clone().requires_grad_()
+    got = run(QuantizedTensorPair(qa, qa_t), qa, w1)
+    assert _lib.gemm_status() == 0
+    for r, g in zip(ref, got):  # same bytes per row and per column block reach the same kernels
+        assert torch.equal(r, g)
+    # without the column copy it is re-quantised from the dequantised rows: same forward, gated weight gradient
+    qa2 = QuantizedTensor.quantize(a.clone().requires_grad_(), E4, MX, axis=-1, block_size=32,
+                                   scaling_recipe=ScalingRecipe(), group_lens=lens)
+    w2 = w.clone().requires_grad_()
+    got2 = run(QuantizedTensorPair(qa2, None), qa2, w2)
+    assert _lib.gemm_status() == 0
+    assert torch.equal(ref[0], got2[0]) and torch.equal(ref[1], got2[1])
+    assert O.rel_frobenius(ref[2].float().cpu(), got2[2].float().cpu()) <= 0.05
