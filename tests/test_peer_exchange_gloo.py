@@ -1,8 +1,8 @@
 """CPU: the peer-memory exchange (primus_turbo_b200/pytorch/dist/peer_exchange.py).
 
-* ``segment_tables`` simulated for every rank of a 2- and a 4-rank job in one process: the dispatch puts
+* ``segment_tables`` simulated for every rank of 2-, 4- and 8-rank jobs in one process: the dispatch puts
   each row at its expert-major position in its expert's owner, the combine brings it back.
-* world sizes 2 and 4 as real processes over gloo: regions live in shared memory, published with the same
+* world sizes 2, 4 and 8 as real processes over gloo (one case with a rank that receives no row at all): regions live in shared memory, published with the same
   handle exchange the GPU path uses, and a copy loop of this test stands in for the device kernel;
   forward and backward against a single-process evaluation, with an expert nobody routes to, and over
   two steps (a region is reused).
@@ -20,14 +20,15 @@ import torch.multiprocessing as mp
 from primus_turbo_b200.pytorch.dist.peer_exchange import segment_tables
 
 H = 8
-SHAPES = [(2, 6), (4, 8), (8, 16)]
+SHAPES = [(2, 6), (4, 8), (8, 16), (4, 4)]  # (4, 4): one expert per rank, so the rank of the unused expert gets no row
 
 
 def _routing(seed, WORLD, E, step=0):
     g = torch.Generator().manual_seed(seed * 10 + step)
     counts = torch.randint(0, 7, (WORLD, E), generator=g)
     counts[:, 1] = 0  # an expert nobody routes to
-    counts[1, 4] = 0
+    if E > 4:
+        counts[1, 4] = 0
     xs = [torch.randn(int(counts[r].sum()), H, generator=g, dtype=torch.float64) for r in range(WORLD)]
     return counts, xs
 
