@@ -11,14 +11,16 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 H = 5
-SHAPES = [(2, 6), (4, 8)]  # (world size, experts): 3 and 2 experts per rank
+# (world size, experts): 3, 2 and 1 experts per rank; with one expert per rank the owner of the unused expert gets no row
+SHAPES = [(2, 6), (4, 8), (4, 4)]
 
 
 def _routing(seed, WORLD, E):
     g = torch.Generator().manual_seed(seed)
     counts = torch.randint(0, 7, (WORLD, E), generator=g)
     counts[:, 1] = 0  # an expert nobody routes to
-    counts[1, 4] = 0
+    if E > 4:
+        counts[1, 4] = 0
     xs = [torch.randn(int(counts[r].sum()), H, generator=g, dtype=torch.float64) for r in range(WORLD)]
     return counts, xs
 
