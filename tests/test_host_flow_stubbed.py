@@ -294,3 +294,45 @@ def test_mx_grouped_activation_as_quantized_tensor(monkeypatch, recorded_calls):
     assert _names(recorded_calls) == ["ptb_quant_mxfp8_grouped", "ptb_grouped_gemm_mxfp8", "ptb_grouped_gemm_mxfp8_variable_k"]
     assert recorded_calls[1][1][13] == M, "dgrad runs over the packed rows"
     assert qa.grad.shape == (M, K) and w.grad.shape == (G, N, K)
+
+
+@pytest.mark.parametrize("granularity", [ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE])
+def test_grouped_gemm_tensorwise_rowwise_with_quantized_operands(monkeypatch, recorded_calls, granularity):
+    """A grouped activation and a weight quantised ahead of time skip exactly their own quantisation."""
+    from primus_turbo_b200.pytorch.core.quantized_tensor import QuantizedTensor
+
+    gemm_impl = sys.modules["primus_turbo_b200.pytorch.kernels.gemm_impl"]
+    grouped = sys.modules["primus_turbo_b200.pytorch.ops.grouped_gemm_fp8"]
+    import importlib
+
+    custom = importlib.import_module("primus_turbo_b200.pytorch.kernels.custom_ops")
+    offsets = lambda lens: torch.cat([lens.new_zeros(1), lens.cumsum(0)])  # noqa: E731
+    for mod in (gemm_impl, grouped, custom):
+        if hasattr(mod, "group_offs_from_lens"):
+            monkeypatch.setattr(mod, "group_offs_from_lens", offsets)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    G, K, N, rows = 2, 256, 384, 200
+    lens = torch.tensor([rows, 0], dtype=torch.int64)
+    cfg = Float8QuantConfig(granularity=granularity)
+
+    def sequence(a_op, w_op):
+        del recorded_calls[:]
+        out = grouped.grouped_gemm_fp8(a_op, w_op, lens, config=cfg)
+        fwd = _names(recorded_calls)
+        del recorded_calls[:]
+        out.backward(torch.zeros((rows, N), dtype=torch.bfloat16))
+        return out, fwd, _names(recorded_calls)
+
+    a = torch.zeros((rows, K), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.zeros((G, N, K), dtype=torch.bfloat16, requires_grad=True)
+    out, fwd_raw, bwd_raw = sequence(a, w)
+    assert out.shape == (rows, N)
+    qa = QuantizedTensor.quantize(a.detach().clone().requires_grad_(), E4, granularity, axis=-1, group_lens=lens)
+    qw = QuantizedTensor.quantize(w.detach().clone().requires_grad_(), E4, granularity, axis=-1)
+    assert qa._is_grouped_tensor and qa.group_offs.tolist() == [0, rows, rows]
+    out, fwd_q, bwd_q = sequence(qa, qw)
+    assert out.shape == (rows, N) and qa.grad.shape == (rows, K) and qw.grad.shape == (G, N, K)
+    # forward: the two operand quantisations are gone, everything after them is unchanged
+    assert fwd_raw[:2] == [fwd_raw[0]] * 2 and fwd_raw[0].startswith("ptb_quant_fp8_")
+    assert fwd_q == fwd_raw[2:] and fwd_q[0] == "ptb_grouped_gemm_fp8"
+    assert bwd_q == bwd_raw

@@ -162,3 +162,31 @@ def test_grouped_activation_as_quantized_tensor():
     assert _lib.gemm_status() == 0
     assert torch.equal(ref[0], got2[0]) and torch.equal(ref[1], got2[1])
     assert O.rel_frobenius(ref[2].float().cpu(), got2[2].float().cpu()) <= 0.05
+
+
+@pytest.mark.parametrize("granularity", [ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE])
+def test_grouped_gemm_tensorwise_rowwise_with_pre_quantised_operands(granularity):
+    """The reference's ``test_grouped_gemm_fp8_{tensorwise,rowwise}_quantized_tensor``: a grouped activation and a
+    weight quantised ahead of time go through the code the raw tensors take after their own quantisation, so the
+    three results are the raw-tensor call's bit for bit."""
+    G, K, N = 4, 256, 384
+    lens = torch.tensor([100, 0, 157, 43], dtype=torch.int64, device=DEV)
+    rows = int(lens.sum())
+    cfg = Float8QuantConfig(granularity=granularity)
+    a, w, gy = _mk((rows, K), 10), _mk((G, N, K), 11, 0.05), _mk((rows, N), 12, 0.01)
+
+    def run(a_op, w_op, a_leaf, w_leaf):
+        out = grouped_gemm_fp8(a_op, w_op, lens, config=cfg)
+        out.backward(gy)
+        return out.detach(), a_leaf.grad, w_leaf.grad
+
+    a0, w0 = a.clone().requires_grad_(), w.clone().requires_grad_()
+    ref = run(a0, w0, a0, w0)
+    qa = QuantizedTensor.quantize(a.clone().requires_grad_(), E4, granularity, axis=-1, group_lens=lens)
+    qw = QuantizedTensor.quantize(w.clone().requires_grad_(), E4, granularity, axis=-1)
+    got = run(qa, qw, qa, qw)
+    assert _lib.gemm_status() == 0
+    for r, g in zip(ref, got):
+        assert torch.equal(r, g)
+    hp = torch.cat([a[o : o + n].float() @ w[i].float().t() for i, (o, n) in enumerate(zip([0, 100, 100, 257], [100, 0, 157, 43]))])
+    assert O.snr_db(hp.cpu(), got[0].float().cpu()) > 25
