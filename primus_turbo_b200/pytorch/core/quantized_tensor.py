@@ -224,7 +224,9 @@ class QuantizedTensor(torch.Tensor):
 
     @property
     def quantized_axis(self):
-        return self._quantized_axis
+        """The axis the scales run along, as a non-negative index into the payload (the reference resolves
+        negative axes the same way, quantized_tensor.py:507-509 there)."""
+        return _norm_axis(self._quantized_axis, self._data.ndim)
 
     @torch.no_grad()
     def dequantize(self) -> torch.Tensor:

@@ -121,13 +121,13 @@ def test_mx_quantized_tensor_layouts(recorded_calls):
         QuantizedTensor.quantize(x, E4, MX, axis=-1, block_size=32)
     row = QuantizedTensor.quantize(x, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe())
     assert row.shape == (96, 160) and row.qdata.shape == (96, 256) and row.scale_inv.shape == (96, 8)
-    assert row.scale_inv.dtype == torch.float8_e8m0fnu and row.quantized_axis == -1
+    assert row.scale_inv.dtype == torch.float8_e8m0fnu and row.quantized_axis == 1
     col = QuantizedTensor.quantize(x, E4, MX, axis=-2, block_size=32, scaling_recipe=ScalingRecipe())
     assert col.shape == (96, 160) and col.qdata.shape == (160, 128) and col.scale_inv.shape == (160, 4)
     assert row.dequantize().shape == (96, 160) and col.dequantize().shape == (96, 160)
     del recorded_calls[:]
     t = row.t()
-    assert t.quantized_axis == -2 and t.qdata.shape == (160, 128) and t.shape == (96, 160)
+    assert t.quantized_axis == 0 and t.qdata.shape == (160, 128) and t.shape == (96, 160)
     assert _names(recorded_calls) == ["ptb_dequant_mxfp8", "ptb_quant_mxfp8"]
     w = torch.zeros((3, 64, 128), dtype=torch.bfloat16)
     qw = QuantizedTensor.quantize(w, E4, MX, axis=-1, block_size=32, scaling_recipe=ScalingRecipe(use_2d_block=True))
@@ -150,7 +150,7 @@ def test_mx_create_quantized_weight(recorded_calls):
     w = torch.zeros((256, 512), dtype=torch.bfloat16, requires_grad=True)
     qw, qw_t = create_quantized_weight(w, E4, _mx_cfg(), need_weight_transpose_cache=True)
     assert qw.scaling_recipe == ScalingRecipe(use_2d_block=True) == qw_t.scaling_recipe
-    assert qw.quantized_axis == -1 and qw_t.quantized_axis == -2
+    assert qw.quantized_axis == 1 and qw_t.quantized_axis == 0
     assert qw.qdata.shape == (256, 512) and qw_t.qdata.shape == (512, 256)
     # both copies are 32x32-tile quantisations: the 2-D flag is argument 9 (row) / 10 (column) of the entry point
     assert [(c[0], c[1][9], c[1][10]) for c in recorded_calls] == [("ptb_quant_mxfp8", 1, 1)] * 2

@@ -141,7 +141,7 @@ def test_quantized_tensor_flatten_unflatten_round_trip():
         "_orig_group_lens", "_orig_group_offs", "_group_lens", "_group_offs"}
     r = QuantizedTensor.__tensor_unflatten__({n: getattr(q, n) for n in names}, meta, q.shape, q.stride())
     assert r.shape == q.shape and r.dtype == torch.float16 and r.real_dtype == torch.float8_e5m2
-    assert r.granularity == ScalingGranularity.ROWWISE and r.quantized_axis == -1 and r._is_grouped_tensor
+    assert r.granularity == ScalingGranularity.ROWWISE and r.quantized_axis == r.qdata.ndim - 1 and r._is_grouped_tensor
     assert r.qdata is q.qdata and r.scale_inv is q.scale_inv and r.group_lens is lens and r.group_offs is offs
     plain = _cpu_qt()
     names, meta = plain.__tensor_flatten__()

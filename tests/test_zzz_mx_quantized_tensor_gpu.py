@@ -57,7 +57,7 @@ def test_payload_matches_the_plain_op_and_round_trips(shape, use_2d):
         # one e4m3 rounding of a value scaled into the block's binade: relative error <= 2^-4 of the block maximum
         assert O.rel_frobenius(x.float().cpu(), back.float().cpu()) <= 0.04
     t = QuantizedTensor.quantize(x, E4, MX, axis=-1, block_size=32, scaling_recipe=recipe).transpose(-2, -1)
-    assert t.quantized_axis == -2 and t.qdata.shape[-2] == shape[-1]
+    assert t.quantized_axis == nd - 2 and t.qdata.shape[-2] == shape[-1]
 
 
 @pytest.mark.parametrize("fmt", [Format.E4M3, Format.HYBRID])
