@@ -24,6 +24,7 @@ float4_e2m1fn_x2 = getattr(torch, "float4_e2m1fn_x2", None)
 MXFP8_BLOCK_SIZE = 32
 MXFP4_BLOCK_SIZE = 32
 MXFP8_PADDING_ALIGN_SIZE = 128
+MXFP4_PADDING_ALIGN_SIZE = 128
 DEFAULT_BLOCK_SIZE = 128
 
 _FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e4m3fnuz, torch.float8_e5m2, torch.float8_e5m2fnuz)
@@ -104,3 +105,12 @@ class Float8QuantConfig:
             assert self.scale_dtype == ScaleDtype.E8M0, (
                 f"scale_dtype should be {ScaleDtype.E8M0} when granularity is MX_BLOCKWISE"
             )
+
+
+class Float4QuantConfig:
+    """Present so that code importing the name keeps importing (low_precision.py:189-214 in the reference);
+    FP4 kernels are not part of this build, so a configuration cannot be made."""
+
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("MXFP4 kernels are not part of this build.")
+
