@@ -148,7 +148,8 @@ def call(name: str, *args) -> None:
         rc = fn(*args)
     check(rc, name)
     launch_count += KERNELS_PER_CALL.get(name, 1)
-    if _DEBUG_STATUS and name in _GEMM_ENTRY_POINTS:
+    if _DEBUG_STATUS and name in _GEMM_ENTRY_POINTS and not torch.cuda.is_current_stream_capturing():
+        # (a stream that is being captured into a graph cannot be waited for: the check is skipped there)
         torch.cuda.synchronize()
         code = gemm_status(reset=True)
         if code != 0:

@@ -190,3 +190,39 @@ def test_grouped_gemm_tensorwise_rowwise_with_pre_quantised_operands(granularity
         assert torch.equal(r, g)
     hp = torch.cat([a[o : o + n].float() @ w[i].float().t() for i, (o, n) in enumerate(zip([0, 100, 100, 257], [100, 0, 157, 43]))])
     assert O.snr_db(hp.cpu(), got[0].float().cpu()) > 25
+
+
+def test_grouped_gemm_replays_from_a_cuda_graph_with_new_group_lens():
+    """The reference's (currently skipped) graph tests, tests/pytorch/ops/test_grouped_gemm_fp8.py:802-929: forward
+    and backward captured once, replayed after ``group_lens`` was rewritten in place.  Nothing on the host
+    depends on the group lengths (offsets, padded layouts and tile schedules are computed on the device), so the
+    replay must give exactly what an eager call with the new lengths gives."""
+    G, K, N, M = 4, 512, 384, 1024
+    cfg = Float8QuantConfig(granularity=ScalingGranularity.BLOCKWISE, block_size=128)
+    a, w, gy = _mk((M, K), 13).requires_grad_(), _mk((G, N, K), 14, 0.05).requires_grad_(), _mk((M, N), 15, 0.01)
+    first, second = [300, 0, 500, 224], [256, 256, 256, 256]
+    lens = torch.tensor(first, dtype=torch.int64, device=DEV)
+
+    def step(group_lens):
+        out = grouped_gemm_fp8(a, w, group_lens, config=cfg)
+        return (out,) + torch.autograd.grad(out, (a, w), gy)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up outside the capture: one-time kernel attributes, allocator pools
+        for _ in range(2):
+            step(lens)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step(lens)
+    for values in (first, second, first):
+        lens.copy_(torch.tensor(values, dtype=torch.int64, device=DEV))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [t.clone() for t in captured]
+        want = step(torch.tensor(values, dtype=torch.int64, device=DEV))
+        torch.cuda.synchronize()
+        assert _lib.gemm_status() == 0
+        for g, e in zip(got, want):
+            assert torch.equal(g, e)
