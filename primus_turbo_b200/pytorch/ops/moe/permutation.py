@@ -13,6 +13,10 @@ forms return the token id of every permuted row (``sorted_indices``).
 
 The routing map is the source of truth for ``token_unpermute``: pass the same ``routing_map`` that
 ``token_permute`` saw (the reference requires it only when merging with probabilities).
+
+``drop_and_pad`` (token-drop routing padded to a fixed capacity per expert) has no kernel in the reference
+either: its only form is the chain of torch ops of :332-349 / :408-436 there, restated here in the same
+terms -- per expert, the first ``capacity`` tokens of a stable descending sort of its 0/1 column.
 """
 
 from __future__ import annotations
@@ -25,6 +29,22 @@ from primus_turbo_b200 import _lib
 from primus_turbo_b200._lib import dtype_code, ptr, require_cuda, stream_of
 
 __all__ = ["token_permute", "token_unpermute"]
+
+
+def capacity_indices(routing_map: torch.Tensor, capacity: int) -> torch.Tensor:
+    """``[num_experts * capacity]`` token ids, expert-major: an expert's routed tokens in token order and, when
+    fewer than ``capacity`` are routed to it, its unrouted tokens in token order after them (a stable
+    descending sort of the expert's 0/1 column cut at ``capacity``)."""
+    by_expert = (routing_map != 0).to(torch.int8).T.contiguous()
+    return by_expert.argsort(dim=-1, descending=True, stable=True)[:, :capacity].contiguous().view(-1)
+
+
+def capacity_probs(probs: torch.Tensor, sorted_indices: torch.Tensor, num_experts: int, capacity: int) -> torch.Tensor:
+    """``probs[token of slot, expert of slot]`` for every slot of ``capacity_indices``' layout."""
+    num_tokens = probs.size(0)
+    expert = torch.arange(num_experts, device=probs.device).unsqueeze(-1)
+    flat = (expert * num_tokens + sorted_indices.view(num_experts, capacity)).view(-1)
+    return probs.T.contiguous().view(-1).index_select(0, flat)
 
 
 def _as_bytes(routing_map: torch.Tensor) -> torch.Tensor:
@@ -127,11 +147,16 @@ def token_permute(
         raise NotImplementedError("not support topk_indices")
     if routing_map is None:
         raise ValueError("must be set topk_indices or routing_map")
-    if drop_and_pad:
-        raise NotImplementedError("drop_and_pad (capacity-padded routing) is not part of this build")
     require_cuda(inp, routing_map)
     assert inp.dim() == 2 and inp.size(0) == routing_map.size(0), "Permute not possible"
     T, E = routing_map.shape
+    if drop_and_pad and not fused and num_out_tokens is not None:  # (the reference's fused form ignores the flag)
+        # every expert takes exactly num_out_tokens / num_experts rows
+        capacity = int(num_out_tokens) // E
+        assert not routing_map.requires_grad
+        sorted_indices = capacity_indices(routing_map, capacity)
+        permuted_probs = capacity_probs(probs, sorted_indices, E, capacity) if probs is not None else None
+        return inp.index_select(0, sorted_indices), permuted_probs, sorted_indices, (routing_map != 0).sum(0)
     if num_out_tokens is None or num_out_tokens < 0:
         capacity = int(_as_bytes(routing_map).sum().item())
     else:
@@ -157,8 +182,20 @@ def token_unpermute(
 ) -> torch.Tensor:
     """Bring expert-major rows back to token order, summing a token's copies (times ``merging_probs[t, e]``
     when given).  ``restore_shape`` = (num_tokens, hidden)."""
-    if drop_and_pad:
-        raise NotImplementedError("drop_and_pad (capacity-padded routing) is not part of this build")
+    if drop_and_pad and not fused:
+        # the slots of a capacity-padded layout are defined by ``sorted_indices`` alone (a padded slot holds a
+        # token that is not routed to the expert), so the rows go back by scatter-add, as in the reference
+        assert restore_shape is not None, "restore_shape must be provided"
+        require_cuda(inp, sorted_indices)
+        input_dtype = inp.dtype
+        if merging_probs is not None:
+            assert routing_map is not None, "Mask must be provided to permute the probs."
+            E = routing_map.size(1)
+            slot_probs = capacity_probs(merging_probs, sorted_indices, E, sorted_indices.size(0) // E)
+            inp = inp * slot_probs.unsqueeze(-1)
+        out = torch.zeros(tuple(restore_shape), dtype=inp.dtype, device=inp.device)
+        out.scatter_add_(0, sorted_indices.unsqueeze(1).expand(-1, inp.size(1)), inp)
+        return out.to(input_dtype)
     assert routing_map is not None, "routing_map must be provided (it defines where every row goes back to)"
     require_cuda(inp, routing_map)
     T = int(restore_shape[0]) if restore_shape is not None else routing_map.shape[0]

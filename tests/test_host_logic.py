@@ -166,3 +166,45 @@ def test_logger_level_once_and_rank_filters(capsys):
     assert err.count("hello 1") == 1 and err.count("only once") == 1
     assert "other rank" not in err and "below the level" not in err
     logger.set_level(logging.WARNING)
+
+
+def test_drop_and_pad_routing_matches_a_slot_by_slot_evaluation(monkeypatch):
+    """Capacity-padded routing (primus_turbo/pytorch/ops/moe/permutation.py:332-349,408-436 in the reference) is
+    a chain of torch ops there and here, so it can be checked on the CPU: every expert takes exactly
+    ``capacity`` slots -- its routed tokens in token order, then unrouted ones in token order -- and the way back
+    adds every slot's row, times the slot's probability, to its token."""
+    import sys
+
+    import primus_turbo_b200.pytorch.ops.moe.permutation  # noqa: F401
+
+    perm = sys.modules["primus_turbo_b200.pytorch.ops.moe.permutation"]
+    monkeypatch.setattr(perm, "require_cuda", lambda *t: None)
+    g = torch.Generator().manual_seed(0)
+    T, E, H, capacity = 11, 4, 6, 3
+    routing = torch.rand(T, E, generator=g) < 0.35
+    routing[:, 2] = False  # an expert nobody routes to: all of its slots are padding
+    routing[:, 0] = True   # more routed tokens than capacity: the later ones are dropped
+    probs = torch.rand(T, E, generator=g, dtype=torch.float64)
+    x = torch.randn(T, H, generator=g, dtype=torch.float64, requires_grad=True)
+    rows, slot_probs, sorted_indices, tpe = perm.token_permute(
+        x, E * capacity, probs=probs, routing_map=routing, drop_and_pad=True)
+    want = []
+    for e in range(E):
+        routed = [t for t in range(T) if routing[t, e]]
+        padding = [t for t in range(T) if not routing[t, e]]
+        want += (routed + padding)[:capacity]
+    assert sorted_indices.tolist() == want and tpe.tolist() == routing.sum(0).tolist()
+    assert torch.equal(rows, x.detach()[want])
+    assert torch.equal(slot_probs, torch.stack([probs[t, i // capacity] for i, t in enumerate(want)]))
+    y = rows * 2.0
+    back = perm.token_unpermute(y, sorted_indices, merging_probs=probs, restore_shape=(T, H), routing_map=routing,
+                                drop_and_pad=True)
+    ref = torch.zeros(T, H, dtype=torch.float64)
+    for i, t in enumerate(want):
+        ref[t] += 2.0 * x.detach()[t] * probs[t, i // capacity]
+    torch.testing.assert_close(back.detach(), ref, rtol=1e-12, atol=1e-12)
+    back.sum().backward()
+    weight = torch.zeros(T, dtype=torch.float64)
+    for i, t in enumerate(want):
+        weight[t] += 2.0 * probs[t, i // capacity]
+    torch.testing.assert_close(x.grad, weight.unsqueeze(1).expand(T, H), rtol=1e-12, atol=1e-12)

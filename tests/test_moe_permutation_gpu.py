@@ -82,7 +82,5 @@ def test_empty_and_argument_errors():
     m = torch.zeros(0, 4, dtype=torch.bool, device=DEV)
     rows, pp, si, tpe = token_permute(x, 0, routing_map=m)
     assert rows.shape == (0, 32) and tpe.tolist() == [0, 0, 0, 0]
-    with pytest.raises(NotImplementedError):
-        token_permute(torch.zeros(2, 32, device=DEV), 2, routing_map=torch.ones(2, 4, device=DEV), drop_and_pad=True)
     with pytest.raises(ValueError):
         token_permute(torch.zeros(2, 32, device=DEV), 2)

@@ -226,3 +226,23 @@ def test_grouped_gemm_replays_from_a_cuda_graph_with_new_group_lens():
         assert _lib.gemm_status() == 0
         for g, e in zip(got, want):
             assert torch.equal(g, e)
+
+
+def test_drop_and_pad_routing_on_the_device():
+    """Capacity-padded routing is a chain of torch ops (as in the reference): the device result must be the host's."""
+    from primus_turbo_b200.pytorch.ops.moe.permutation import capacity_indices, token_permute, token_unpermute
+
+    g = torch.Generator().manual_seed(0)
+    T, E, H, capacity = 300, 8, 64, 20
+    routing = torch.rand(T, E, generator=g) < 0.1
+    probs = torch.rand(T, E, generator=g)
+    x = torch.randn(T, H, generator=g)
+    rows, slot_probs, sorted_indices, tpe = token_permute(
+        x.to(DEV), E * capacity, probs=probs.to(DEV), routing_map=routing.to(DEV), drop_and_pad=True)
+    want = capacity_indices(routing, capacity)
+    assert torch.equal(sorted_indices.cpu(), want) and tpe.cpu().tolist() == routing.sum(0).tolist()
+    assert torch.equal(rows.cpu(), x[want])
+    back = token_unpermute(rows, sorted_indices, merging_probs=probs.to(DEV), restore_shape=(T, H),
+                           routing_map=routing.to(DEV), drop_and_pad=True)
+    ref = torch.zeros(T, H).index_add_(0, want, x[want] * slot_probs.cpu().unsqueeze(1))
+    torch.testing.assert_close(back.cpu(), ref, rtol=1e-5, atol=1e-5)
